@@ -1,0 +1,173 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own eager classes.
+
+Run where a checkout of youngchan2/Trinity is mounted:
+
+    python tests/golden/make_golden.py --ref /path/to/Trinity
+
+For each eager attention class of ``baseline/ref_rms.py`` (``Vanilla`` :28, ``PreNorm`` :84,
+``KeyFormer`` :128, ``NormKeyFormer`` :173, ``QKNorm`` :221, ``NormQKNorm`` :267, ``RoCo`` :317,
+``NormRoCo`` :360) and for ``SimpleFFN`` (``baseline/ffn_ref.py:12``) and the Falcon
+``TensorOpsModel.forward`` body (``ffn_ref.py:86-123``) it runs the class in fp32 on the
+parity driver's seeded inputs (``convert_eval_rms.py:127-176``: seed 42, ``randn*0.01``) and
+stores:
+
+* ``small_*.npz``  -- tiny shapes, inputs AND outputs (self-contained);
+* ``refshape_*.npz`` -- the reference's own shapes (Llama M16 N4096 D128 P1024, Falcon
+  M16 N4544 D64 P1024): outputs plus a fingerprint of the regenerated inputs (the inputs
+  are hundreds of MB and are rebuilt from the seed by ``oracle.ref_attention_inputs``).
+
+The eager classes compute the KeyFormer / RoCo per-key tensors and drop them
+(``ref_rms.py:166``, ``:351-352``); they are captured here by recording what the class
+passes through ``F.softmax`` and applying the class's own reduction lines.
+"""
+from __future__ import annotations
+
+import argparse
+import ast
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import oracle as orc          # noqa: E402
+from oracle.ref_shim import load_reference  # noqa: E402
+
+
+def fingerprint(t: dict) -> np.ndarray:
+    """A few numbers that change if the seeded generator ever produces different inputs."""
+    vals = []
+    for name in sorted(t):
+        x = t[name].flatten()
+        vals += [float(x.double().sum()), float(x[0]), float(x[-1]), float(x[x.numel() // 2])]
+    return np.asarray(vals, dtype=np.float64)
+
+
+class SoftmaxTap:
+    """Record every tensor the reference class sends through ``F.softmax``."""
+
+    def __init__(self, mod):
+        self.mod, self.seen = mod, []
+
+    def __enter__(self):
+        self.real = self.mod.F.softmax
+
+        def tapped(*a, **k):
+            y = self.real(*a, **k)
+            self.seen.append(y)
+            return y
+
+        self.mod.F.softmax = tapped
+        return self
+
+    def __exit__(self, *exc):
+        self.mod.F.softmax = self.real
+
+
+def run_attention(ref_rms, cls_name, M, N, D, P, inp):
+    cls = getattr(ref_rms, cls_name)
+    kw = dict(W_q=inp["WQ"], W_k=inp["WK"], W_v=inp["WV"])
+    if "KeyFormer" in cls_name:
+        model = cls(M, N, D, P, inp["noise"], inp["K_cache"].clone(), inp["V_cache"].clone(), **kw)
+    else:
+        model = cls(M, N, D, P, inp["K_cache"].clone(), inp["V_cache"].clone(), **kw)
+    with SoftmaxTap(ref_rms) as tap, torch.no_grad():
+        o2 = model(inp["X"])
+    out = {"O2": o2}
+    if "KeyFormer" in cls_name:
+        weights, perturb_out = tap.seen           # ref_rms.py:165-166
+        out["C_out"] = perturb_out.sum(dim=1)     # query-axis sum of the emitted kernel
+    if "RoCo" in cls_name:
+        (weights,) = tap.seen
+        out["C_out1"] = weights.sum(dim=1)        # ref_rms.py:351
+        out["C_out2"] = weights.pow(2).sum(dim=1)  # ref_rms.py:352
+    return out
+
+
+def falcon_tail_class(ref_root):
+    """Compile the nested ``TensorOpsModel`` of ``TRT_Falcon_Ffn.build_engine`` from its source."""
+    path = os.path.join(ref_root, "baseline", "ffn_ref.py")
+    tree = ast.parse(open(path).read())
+    for node in ast.walk(tree):
+        if isinstance(node, ast.ClassDef) and node.name == "TRT_Falcon_Ffn":
+            for sub in ast.walk(node):
+                if isinstance(sub, ast.ClassDef) and sub.name == "TensorOpsModel":
+                    module = ast.Module(body=[sub], type_ignores=[])
+                    ns = {"nn": torch.nn, "torch": torch}
+                    exec(compile(module, path, "exec"), ns)
+                    return ns["TensorOpsModel"]
+    raise RuntimeError("TensorOpsModel not found")
+
+
+ATTN_CLASSES = ["Vanilla", "PreNorm", "KeyFormer", "NormKeyFormer", "QKNorm", "NormQKNorm", "RoCo", "NormRoCo"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    ref_rms, ffn_ref = load_reference(args.ref)
+    torch.set_num_threads(os.cpu_count())
+
+    # ---- small, self-contained ----
+    for tag, (M, N, D, P) in {"a": (16, 128, 32, 48), "b": (8, 256, 128, 0), "c": (5, 192, 64, 33)}.items():
+        inp = orc.ref_attention_inputs(M, N, D, P, seed=42, std=0.2)
+        blob = {"shape": np.asarray([M, N, D, P])}
+        blob.update({"in_" + k: v.numpy() for k, v in inp.items()})
+        for cls in ATTN_CLASSES:
+            for name, val in run_attention(ref_rms, cls, M, N, D, P, inp).items():
+                blob[f"{cls}.{name}"] = val.numpy()
+        np.savez_compressed(os.path.join(HERE, f"small_attn_{tag}.npz"), **blob)
+        print("wrote small_attn_" + tag)
+
+    for tag, (M, N, P) in {"a": (16, 128, 256), "b": (7, 96, 160)}.items():
+        inp = orc.ref_ffn_inputs(M, N, P, seed=42, std=0.3)
+        blob = {"shape": np.asarray([M, N, P])}
+        blob.update({"in_" + k: v.numpy() for k, v in inp.items()})
+        ffn = ffn_ref.SimpleFFN(M, N, P, WO=inp["WO"], WFF1a=inp["WFF1a"], WFF1b=inp["WFF1b"], WFF2=inp["WFF2"])
+        with torch.no_grad():
+            blob["SimpleFFN.FF2"] = ffn(inp["O2"], inp["X"]).numpy()
+        np.savez_compressed(os.path.join(HERE, f"small_ffn_{tag}.npz"), **blob)
+        print("wrote small_ffn_" + tag)
+
+    # Falcon tail: square weights, divisor hard-coded to 4544 in the reference body
+    Tail = falcon_tail_class(args.ref)
+    M, N = 16, 128
+    inp = orc.ref_ffn_inputs(M, N, N, seed=42, std=0.3)
+    tail = Tail(N, inp["WO"], inp["WFF1a"], inp["WFF1b"], inp["WFF2"])
+    with torch.no_grad():
+        o = tail(inp["O2"], inp["X"])
+    blob = {"shape": np.asarray([M, N, N]), "FalconTail.O_FF_norm": o.numpy()}
+    blob.update({"in_" + k: v.numpy() for k, v in inp.items()})
+    np.savez_compressed(os.path.join(HERE, "small_ffn_falcon_tail.npz"), **blob)
+    print("wrote small_ffn_falcon_tail")
+
+    # ---- the reference's own shapes: outputs + input fingerprint ----
+    for model, (M, N, D, P), classes in [
+        ("llama", (16, 4096, 128, 1024), ["Vanilla", "NormKeyFormer", "NormQKNorm", "RoCo"]),
+        ("falcon", (16, 4544, 64, 1024), ["PreNorm", "KeyFormer"]),
+    ]:
+        inp = orc.ref_attention_inputs(M, N, D, P, seed=42)
+        blob = {"shape": np.asarray([M, N, D, P]), "fingerprint": fingerprint(inp)}
+        for cls in classes:
+            for name, val in run_attention(ref_rms, cls, M, N, D, P, inp).items():
+                blob[f"{cls}.{name}"] = val.numpy()
+        np.savez_compressed(os.path.join(HERE, f"refshape_attn_{model}.npz"), **blob)
+        print("wrote refshape_attn_" + model)
+
+    M, N, P = 16, 4096, 14336
+    inp = orc.ref_ffn_inputs(M, N, P, seed=42)
+    ffn = ffn_ref.SimpleFFN(M, N, P, WO=inp["WO"], WFF1a=inp["WFF1a"], WFF1b=inp["WFF1b"], WFF2=inp["WFF2"])
+    with torch.no_grad():
+        ff2 = ffn(inp["O2"], inp["X"])
+    np.savez_compressed(os.path.join(HERE, "refshape_ffn_llama.npz"), shape=np.asarray([M, N, P]),
+                        fingerprint=fingerprint(inp), **{"SimpleFFN.FF2": ff2.numpy()})
+    print("wrote refshape_ffn_llama")
+
+
+if __name__ == "__main__":
+    main()
