@@ -1,0 +1,169 @@
+/* trinity_b200 -- C ABI of the B200 (sm_100a) fused transformer blocks.
+ *
+ * The library replaces the device code behind the "generated module" operator API of
+ * youngchan2/Trinity: a Python module exposing TENSOR_PARAMS, BLOCK_PARAMS and
+ * forward(*tensors, block_*=16) (codegen/TritonGen.py:543-716), whose forward() launches the
+ * Triton kernels kernel_0..kernel_k that TritonGen emitted.  Here forward() calls ONE of the entry
+ * points below instead.  All pointers are DEVICE pointers borrowed for the duration of the call;
+ * tensors are row-major and contiguous; `stream` is a cudaStream_t passed as void*.
+ *
+ * Conventions: return 0 (TB200_OK) or a negative tb200_status; never throw; never allocate device
+ * memory, never synchronise the device (safe under CUDA-graph capture once the first call on a
+ * device has run outside capture); workspace is supplied by the caller and sized by the
+ * *_workspace_bytes() queries.  Argument checks (null, shape, 16-byte alignment) are done on the
+ * host before anything is launched.
+ */
+#ifndef TRINITY_B200_H_
+#define TRINITY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TB200_OK = 0,
+  TB200_ERR_INVALID = -1,        /* null pointer, bad shape, misaligned pointer */
+  TB200_ERR_UNSUPPORTED = -2,    /* a legal request this build has no kernel for */
+  TB200_ERR_CUDA = -3,           /* a CUDA runtime/driver call failed */
+  TB200_ERR_WORKSPACE = -4,      /* workspace missing or too small */
+  TB200_ERR_DEVICE_TIMEOUT = -5  /* a bounded device-side wait gave up (see tb200_device_status) */
+} tb200_status;
+
+typedef enum { TB200_F16 = 0, TB200_BF16 = 1, TB200_F32 = 2 } tb200_dtype;
+
+const char* tb200_strerror(int status);
+/* Library/ABI version: major*1000 + minor. */
+int tb200_version(void);
+/* Reads (and clears) the device-side error word of the current device; 0 = no kernel gave up a wait.
+ * Synchronises the device -- a debugging / test aid, not part of the hot path. */
+int tb200_device_status(int* code_out);
+
+/* ---------------------------------------------------------------------------------------------
+ * RMSNorm: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) [* weight].
+ * Replaces the standalone RMSNorm kernels of evaluation/ffn/ffn_falcon/rms_ref.py:13-71; math of
+ * baseline/ref_rms.py:101-102 (reference point: weight = NULL, eps = 0).
+ * y may be NULL (statistics only); inv_rms (fp32, one per row) may be NULL.  cols % 8 == 0. */
+int tb200_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
+                  float eps, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused GEMM  C = epilogue(A[m,k] @ B[k,n]),  16-bit inputs, fp32 accumulation on tcgen05/TMEM.
+ * The building block behind the k-loops of every emitted kernel (e.g.
+ * evaluation/ffn/ffn_llama/ffn_llama_benchmark2248.py:19-62 "O2*WO + X", :80-130 gate/up + SiLU,
+ * :148-185 down projection).  Epilogue, in this order:  acc *= row_scale[m]  (norm-as-epilogue,
+ * evaluation/prenorm/prenorm_falcon_benchmark579.py:86-88);  dual: silu(acc_b) * acc_b2  (SwiGLU);
+ * act: 1 = exact-erf GELU;  + residual[m,n]. */
+typedef struct {
+  int dtype;               /* TB200_F16 or TB200_BF16: a, b, b2, c, residual */
+  int act;                 /* 0 none, 1 GELU (erf) */
+  int64_t m, n, k;         /* n % 8 == 0, k % 8 == 0 */
+  const void* a;           /* (m,k) */
+  const void* b;           /* (k,n) */
+  const void* b2;          /* (k,n) or NULL: when set, c = silu(a@b) * (a@b2) */
+  void* c;                 /* (m,n) */
+  const float* row_scale;  /* (m) or NULL */
+  const void* residual;    /* (m,n) or NULL */
+  int split_k;             /* 0 = let the library choose; 1 = never split; >1 = that many K slices */
+  void* workspace;         /* needed when K is split (fp32 partial sums) */
+  size_t workspace_bytes;
+} tb200_gemm_args;
+size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
+int tb200_gemm(const tb200_gemm_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused attention block -- replaces kernel_0/kernel_1 of the emitted attention modules:
+ *   Vanilla   evaluation/vanilla/vanilla_falcon_benchmark28173.py:19-144  (baseline/ref_rms.py:44-82)
+ *   PreNorm   evaluation/prenorm/prenorm_falcon_benchmark579.py:19-120    (ref_rms.py:100-126)
+ *   QKNorm    evaluation/qknorm/qknorm_falcon_benchmark1350.py:19-116     (ref_rms.py:237-265)
+ *   KeyFormer evaluation/keyformer/keyformer_falcon_benchmark4358.py:19-147 (ref_rms.py:146-171)
+ *   RoCo      evaluation/roco/roco_falcon_benchmark1620.py:19-141         (ref_rms.py:333-357)
+ * [x -> RMSNorm] -> q,k,v = x@W{q,k,v} -> split heads -> [per-head RMSNorm of q,k] -> append k,v to the
+ * cache rows [past,past+seq) -> softmax(scale * q@K^T [causal]) @ V -> merge heads into o2; optional
+ * per-key reductions and top-k.  Reference parameter point: batch 1, n_kv_heads == n_q_heads,
+ * sm_scale 1, no CAUSAL flag, all weights NULL, eps 0, tau 1.5. */
+enum {
+  TB200_ATTN_PRENORM = 1,    /* RMSNorm over hidden before the projections */
+  TB200_ATTN_QKNORM = 2,     /* per-head RMSNorm of q and k (normalised k is what is cached) */
+  TB200_ATTN_CAUSAL = 4,     /* query i sees keys <= past + i */
+  TB200_ATTN_KEYFORMER = 8,  /* c_out[b,h,j] = sum_i softmax_j((scale*s + noise)/tau)[i,j] */
+  TB200_ATTN_ROCO = 16       /* c_out1 = sum_i p[i,j], c_out2 = sum_i p[i,j]^2 */
+};
+typedef struct {
+  int dtype;                 /* TB200_F16 / TB200_BF16: x, weights, caches, o2, norm weights, noise */
+  int flags;
+  int batch, seq, hidden;    /* B, S (new tokens per sequence), N */
+  int n_q_heads, n_kv_heads, head_dim; /* head_dim 64 or 128 */
+  int past;                  /* P: rows already valid in the caches */
+  int cache_len;             /* rows allocated per head in the caches, >= past + seq */
+  float sm_scale, norm_eps, qk_eps, tau;
+  const void* x;             /* (B,S,N) */
+  const void* wq;            /* (N, Hq*D) */
+  const void* wk;            /* (N, Hkv*D) */
+  const void* wv;            /* (N, Hkv*D) */
+  void* k_cache;             /* (B,Hkv,cache_len,D); rows [past,past+seq) are written */
+  void* v_cache;
+  void* o2;                  /* (B,S,Hq*D) */
+  const void* norm_weight;   /* (N) or NULL */
+  const void* q_norm_weight; /* (D) or NULL */
+  const void* k_norm_weight; /* (D) or NULL */
+  const void* noise;         /* (B,Hq,S,past+seq), KEYFORMER */
+  void* c_out;               /* (B,Hq,past+seq), KEYFORMER */
+  void* c_out1;              /* (B,Hq,past+seq), ROCO */
+  void* c_out2;
+  int aux_dtype;             /* dtype of c_out*: TB200_F32 or the 16-bit dtype */
+  int topk;                  /* 0 = none; else indices of the k largest per-key scores per (b,h): */
+  int32_t* topk_idx;         /* (B,Hq,topk), stable descending (ties -> lower index); key = c_out
+                                (KEYFORMER) or c_out1 (ROCO) as fp32 before any narrowing */
+  void* workspace;
+  size_t workspace_bytes;
+} tb200_attn_args;
+size_t tb200_attn_workspace_bytes(const tb200_attn_args* args);
+int tb200_attn_forward(const tb200_attn_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused FFN block -- replaces kernel_0..2 of evaluation/ffn/ffn_llama/ffn_llama_benchmark2248.py:19-258
+ * and kernel_0..4 of evaluation/ffn/ffn_falcon/ffn_benchmark428.py:19-233 (baseline/ffn_ref.py:24-52,
+ * :86-123):  a = [o2 @ wo + residual_x | x];  h = [RMSNorm(a) | a];
+ * ff2 = act(h @ w_gate [, h @ w_up]) @ w_down;  [o_ff = ff2 + h; o_ff_norm = RMSNorm(o_ff)]. */
+enum { TB200_FFN_SWIGLU = 0, TB200_FFN_GELU = 1 };
+enum {
+  TB200_FFN_NORM = 1,        /* RMSNorm of a before the up projections */
+  TB200_FFN_FALCON_TAIL = 2  /* o_ff = ff2 + h, o_ff_norm = o_ff / sqrt(sum(o_ff^2)/tail_divisor) */
+};
+typedef struct {
+  int dtype;
+  int act;                   /* TB200_FFN_SWIGLU or TB200_FFN_GELU */
+  int flags;
+  int64_t tokens, hidden, inner; /* M, N, P */
+  float norm_eps;
+  int tail_divisor;          /* 0 = hidden (the reference hard-codes 4544) */
+  const void* x;             /* (M,N): the block input, or the residual when wo is set */
+  const void* o2;            /* (M,N) or NULL: attention output fed through wo */
+  const void* wo;            /* (N,N) or NULL */
+  const void* norm_weight;   /* (N) or NULL */
+  const void* w_gate;        /* (N,P): WFF1b (SwiGLU gate) or W1 (GELU) */
+  const void* w_up;          /* (N,P): WFF1a; NULL for GELU */
+  const void* w_down;        /* (P,N): WFF2 */
+  void* ff2;                 /* (M,N) out */
+  void* attn_o2;             /* (M,N) out or NULL: a */
+  void* ff1;                 /* (M,P) out or NULL: activated inner tensor (else kept in workspace) */
+  void* o_ff_norm;           /* (M,N) out, FALCON_TAIL */
+  void* workspace;
+  size_t workspace_bytes;
+} tb200_ffn_args;
+size_t tb200_ffn_workspace_bytes(const tb200_ffn_args* args);
+int tb200_ffn_forward(const tb200_ffn_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Deterministic top-k over the last axis of scores (rows, n) fp32: idx[r,:] = the first k entries of
+ * a stable descending sort (ties -> lower index).  New relative to the reference (which never
+ * selects keys); n <= 16384, 1 <= k <= n. */
+int tb200_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRINITY_B200_H_ */

@@ -1,0 +1,551 @@
+// Fused GEMM on tcgen05: C = epilogue(A[M,K] @ B[K,N]), 16-bit operands, fp32 accumulation in TMEM.
+//
+// Persistent, warp-specialised kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer: A tile (128 x 64, K-major) and four B boxes (64 K-rows x 64 columns each,
+//               MN-major because the weights are stored (K,N) row-major) into a 4-stage ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16, accumulators in TMEM
+//               (two 256-column accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 2-5   epilogue: tcgen05.ld (thread = output row, 32 columns at a time) -> fused epilogue -> global
+// No cluster launch and no multicast: every CTA fetches its own operands; reuse comes from L2, for which
+// the tile order walks groups of kGroupM row-tiles across all column tiles.
+//
+// The four B boxes of a stage may come from different weight tensors:
+//   GEMM_STORE / GEMM_PARTIAL  one source, 256 consecutive columns
+//   GEMM_SWIGLU                gate columns [n0,n0+128) and up columns [n0,n0+128) -> silu(g)*u, 128 wide
+//   GEMM_QKV                   tiles walk Wq, then Wk, then Wv; the epilogue splits heads, optionally
+//                              RMS-normalises each head of q and k, writes q head-major and appends k, v
+//                              to the caches
+#include <string.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;         // 16 KiB
+constexpr int kBChunkBytes = BK * 64 * 2;    // 8 KiB: 64 K-rows of 64 columns
+constexpr int kBBytes = 4 * kBChunkBytes;    // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kBarrierBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + slack to align the ring to 1 KiB
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;
+constexpr int kTmemCols = 512;
+
+struct GemmParams {
+  CUtensorMap map_a;
+  CUtensorMap map_b[3];
+  int M, K, k_blocks, split_k, kb_per_split;
+  int n_src;
+  int src_n[3];       // columns of each source
+  int src_tile0[4];   // first column-tile of each source (prefix sums); [n_src] = number of column tiles
+  int tile_n;         // output columns per tile (256, or 128 for SwiGLU)
+  int m_tiles, n_tiles, total_units;
+  int* err;
+  // epilogue
+  const float* row_scale;
+  void* C;
+  long long ldc;
+  const void* residual;
+  long long ldr;
+  void* C2;
+  int act;
+  void* q_out;
+  void* k_cache;
+  void* v_cache;
+  int S, Hq, Hkv, D, past, cache_len, qknorm;
+  float qk_eps;
+  const void* q_norm_weight;
+  const void* k_norm_weight;
+  float* partial;
+  long long ldp;
+};
+
+struct Unit {
+  int m0, src, n0, kb_begin, kb_end, split;
+};
+
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
+  Unit r;
+  const int tile = u / p.split_k;
+  r.split = u - tile * p.split_k;
+  // groups of kGroupM row-tiles walk all column tiles before moving down: A and B stay L2-resident
+  const int per_group = kGroupM * p.n_tiles;
+  const int g = tile / per_group;
+  const int rem = tile - g * per_group;
+  const int rows_here = min(kGroupM, p.m_tiles - g * kGroupM);
+  const int nt = rem / rows_here;
+  const int mt = g * kGroupM + (rem - nt * rows_here);
+  r.m0 = mt * BM;
+  int src = 0;
+  while (src + 1 < p.n_src && nt >= p.src_tile0[src + 1]) ++src;
+  if (p.tile_n != BN) src = 0;  // SwiGLU: both sources are walked together
+  r.src = src;
+  r.n0 = (nt - p.src_tile0[src]) * p.tile_n;
+  r.kb_begin = r.split * p.kb_per_split;
+  r.kb_end = min(p.k_blocks, r.kb_begin + p.kb_per_split);
+  return r;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+template <typename T>
+__device__ __forceinline__ void store32(T* dst, const float (&v)[32]) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    d[i] = make_uint4(Pack2<T>::pack(v[8 * i + 0], v[8 * i + 1]), Pack2<T>::pack(v[8 * i + 2], v[8 * i + 3]),
+                      Pack2<T>::pack(v[8 * i + 4], v[8 * i + 5]), Pack2<T>::pack(v[8 * i + 6], v[8 * i + 7]));
+  }
+}
+// columns valid in steps of 8 (every N is a multiple of 8)
+template <typename T>
+__device__ __forceinline__ void store32_clipped(T* dst, const float (&v)[32], int valid) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (8 * i < valid)
+      d[i] = make_uint4(Pack2<T>::pack(v[8 * i + 0], v[8 * i + 1]), Pack2<T>::pack(v[8 * i + 2], v[8 * i + 3]),
+                        Pack2<T>::pack(v[8 * i + 4], v[8 * i + 5]), Pack2<T>::pack(v[8 * i + 6], v[8 * i + 7]));
+  }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tfull = empty + kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&p.map_a);
+    for (int s = 0; s < p.n_src; ++s) tma_prefetch_desc(&p.map_b[s]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const AbortCtx ctx{p.err, abort_flag};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x) {
+      const Unit t = decode_unit(p, u);
+      for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, ctx, 101)) { ok = false; break; }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&full[stage], kStageBytes);
+          tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            int src = t.src, col = t.n0 + 64 * c;
+            if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
+            tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, BM, BN);
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x) {
+      const Unit t = decode_unit(p, u);
+      if (!mbar_wait(&tempty[acc], acc_phase ^ 1, ctx, 102)) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
+        if (!mbar_wait(&full[stage], phase, ctx, 103)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a0 = smem_u32(smem + stage * kStageBytes);
+          const uint32_t b0 = a0 + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc(a0 + k * 32, 16, 1024);            // K-major: +32 B per 16 K
+            const uint64_t bd = make_smem_desc(b0 + k * 2048, kBChunkBytes, 1024);  // MN-major: +16 K-rows
+            umma_ss(d_tmem, ad, bd, idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);                       // frees the stage when these MMAs have read it
+          if (kb == t.kb_end - 1) umma_commit(&tfull[acc]);  // accumulator complete
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
+      const Unit t = decode_unit(p, u);
+      if (!mbar_wait(&tfull[acc], acc_phase, ctx, 104)) break;
+      tc_fence_after();
+      const int row = t.m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.f;
+      uint32_t r[32];
+      float v[32];
+
+      if (MODE == GEMM_STORE) {
+        const int n_total = p.src_n[0];
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.n0 + c * 32;
+          if (col >= n_total) break;  // warp-uniform
+          tmem_ld_x32(taddr + c * 32, r);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float f = __uint_as_float(r[i]) * rs;
+              if (p.act == 1) f = gelu_erf(f);
+              v[i] = f;
+            }
+            const int valid = min(32, n_total - col);
+            if (p.C2 != nullptr) store32_clipped<T>(static_cast<T*>(p.C2) + row * p.ldc + col, v, valid);
+            if (p.residual != nullptr) {
+              const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + col);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (8 * i < valid) {
+                  const uint4 q4 = __ldg(rp + i);
+                  const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f2 = Pack2<T>::unpack(w[j]);
+                    v[8 * i + 2 * j] += f2.x;
+                    v[8 * i + 2 * j + 1] += f2.y;
+                  }
+                }
+              }
+            }
+            store32_clipped<T>(static_cast<T*>(p.C) + row * p.ldc + col, v, valid);
+          }
+        }
+      } else if (MODE == GEMM_SWIGLU) {
+        const int n_total = p.src_n[0];
+        uint32_t r2[32];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          const int col = t.n0 + c * 32;
+          if (col >= n_total) break;
+          tmem_ld_x32(taddr + c * 32, r);         // gate
+          tmem_ld_x32(taddr + 128 + c * 32, r2);  // up
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = silu(__uint_as_float(r[i]) * rs) * (__uint_as_float(r2[i]) * rs);
+            store32_clipped<T>(static_cast<T*>(p.C) + row * p.ldc + col, v, min(32, n_total - col));
+          }
+        }
+      } else if (MODE == GEMM_PARTIAL) {
+        int n_total = 0, col_base = 0;
+        for (int s = 0; s < p.n_src; ++s) {
+          if (s < t.src) col_base += p.src_n[s];
+        }
+        n_total = p.src_n[t.src];
+        float* prow = p.partial + (static_cast<long long>(t.split) * p.M + row) * p.ldp + col_base;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.n0 + c * 32;
+          if (col >= n_total) break;
+          tmem_ld_x32(taddr + c * 32, r);
+          tmem_wait_ld();
+          if (row_ok) {
+            const int valid = min(32, n_total - col);
+            uint4* d = reinterpret_cast<uint4*>(prow + col);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (4 * i < valid) d[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          }
+        }
+      } else {  // GEMM_QKV
+        const int D = p.D;
+        const int n_total = p.src_n[t.src];
+        const int b = row_ok ? row / p.S : 0;
+        const int s_in = row_ok ? row - b * p.S : 0;
+        const int heads_here = BN / D;  // 2 (D=128) or 4 (D=64) heads per tile
+        const bool norm_this = p.qknorm && t.src < 2;
+        const T* nw = static_cast<const T*>(t.src == 0 ? p.q_norm_weight : p.k_norm_weight);
+#pragma unroll 1
+        for (int hh = 0; hh < heads_here; ++hh) {
+          const int col_h = t.n0 + hh * D;
+          if (col_h >= n_total) break;
+          const int head = col_h / D;
+          float scale = rs;
+          if (norm_this) {  // pass 1: sum of squares over the head's D columns (thread-local: a thread owns a row)
+            float ss = 0.f;
+            for (int c = 0; c < D / 32; ++c) {
+              tmem_ld_x32(taddr + hh * D + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float f = __uint_as_float(r[i]) * rs;
+                ss = fmaf(f, f, ss);
+              }
+            }
+            scale = rs * rsqrtf(ss / static_cast<float>(D) + p.qk_eps);
+          }
+          T* dst;
+          if (t.src == 0) {
+            dst = static_cast<T*>(p.q_out) + ((static_cast<long long>(b) * p.Hq + head) * p.S + s_in) * D;
+          } else {
+            T* cache = static_cast<T*>(t.src == 1 ? p.k_cache : p.v_cache);
+            dst = cache + ((static_cast<long long>(b) * p.Hkv + head) * p.cache_len + p.past + s_in) * D;
+          }
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld_x32(taddr + hh * D + c * 32, r);
+            tmem_wait_ld();
+            if (row_ok) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
+              if (norm_this && nw != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  const float2 g = Pack2<T>::unpack(*reinterpret_cast<const uint32_t*>(nw + c * 32 + i));
+                  v[i] *= g.x;
+                  v[i + 1] *= g.y;
+                }
+              }
+              store32<T>(dst + c * 32, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ split-K finish
+template <typename T>
+__global__ void splitk_finish_kernel(SplitKFinish f) {
+  const int64_t groups_per_row = f.N / 8;
+  const int64_t total = static_cast<int64_t>(f.M) * groups_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / groups_per_row;
+    const int col = static_cast<int>(i - row * groups_per_row) * 8;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < f.split_k; ++s) {  // fixed order: deterministic
+      const float* p = f.partial + (static_cast<int64_t>(s) * f.M + row) * f.ldp + col;
+      const float4 x0 = *reinterpret_cast<const float4*>(p), x1 = *reinterpret_cast<const float4*>(p + 4);
+      a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
+      if (f.gated) {
+        const float4 y0 = *reinterpret_cast<const float4*>(p + f.N), y1 = *reinterpret_cast<const float4*>(p + f.N + 4);
+        b[0] += y0.x; b[1] += y0.y; b[2] += y0.z; b[3] += y0.w; b[4] += y1.x; b[5] += y1.y; b[6] += y1.z; b[7] += y1.w;
+      }
+    }
+    const float rs = f.row_scale ? f.row_scale[row] : 1.f;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float x = a[j] * rs;
+      if (f.gated) x = silu(x) * (b[j] * rs);
+      if (f.act == 1) x = gelu_erf(x);
+      v[j] = x;
+    }
+    if (f.C2)
+      *reinterpret_cast<uint4*>(static_cast<T*>(f.C2) + row * f.ldc + col) =
+          make_uint4(Pack2<T>::pack(v[0], v[1]), Pack2<T>::pack(v[2], v[3]), Pack2<T>::pack(v[4], v[5]), Pack2<T>::pack(v[6], v[7]));
+    if (f.residual) {
+      const uint4 q4 = *reinterpret_cast<const uint4*>(static_cast<const T*>(f.residual) + row * f.ldr + col);
+      const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f2 = Pack2<T>::unpack(w[j]);
+        v[2 * j] += f2.x;
+        v[2 * j + 1] += f2.y;
+      }
+    }
+    *reinterpret_cast<uint4*>(static_cast<T*>(f.C) + row * f.ldc + col) =
+        make_uint4(Pack2<T>::pack(v[0], v[1]), Pack2<T>::pack(v[2], v[3]), Pack2<T>::pack(v[4], v[5]), Pack2<T>::pack(v[6], v[7]));
+  }
+}
+
+template <typename T, int MODE>
+int launch_mode(const GemmParams& p, int grid, cudaStream_t stream) {
+  static bool attr_set[32] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 31]) {
+    if (cudaFuncSetAttribute(gemm_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return TB200_ERR_CUDA;
+    attr_set[dev & 31] = true;
+  }
+  gemm_kernel<T, MODE><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
+
+template <typename T>
+int launch_typed(const GemmParams& p, int mode, int grid, cudaStream_t stream) {
+  switch (mode) {
+    case GEMM_STORE: return launch_mode<T, GEMM_STORE>(p, grid, stream);
+    case GEMM_SWIGLU: return launch_mode<T, GEMM_SWIGLU>(p, grid, stream);
+    case GEMM_QKV: return launch_mode<T, GEMM_QKV>(p, grid, stream);
+    case GEMM_PARTIAL: return launch_mode<T, GEMM_PARTIAL>(p, grid, stream);
+    default: return TB200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+
+int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  if (g.dtype != TB200_BF16 && g.dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
+  if (g.A == nullptr || g.M < 0 || g.K <= 0 || (g.K & 7) != 0 || g.n_src < 1 || g.n_src > 3) return TB200_ERR_INVALID;
+  if (!aligned16(g.A)) return TB200_ERR_INVALID;
+  if (g.M == 0) return TB200_OK;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = g.M;
+  p.K = g.K;
+  p.k_blocks = (g.K + BK - 1) / BK;
+  p.split_k = (g.mode == GEMM_PARTIAL) ? g.split_k : 1;
+  if (p.split_k < 1 || p.split_k > p.k_blocks) return TB200_ERR_INVALID;
+  p.kb_per_split = (p.k_blocks + p.split_k - 1) / p.split_k;
+  p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty slice
+  p.n_src = g.n_src;
+  p.tile_n = (g.mode == GEMM_SWIGLU) ? 128 : BN;
+  p.m_tiles = (g.M + BM - 1) / BM;
+  int tiles = 0;
+  for (int s = 0; s < g.n_src; ++s) {
+    if (g.B[s] == nullptr || g.N[s] <= 0 || (g.N[s] & 7) != 0 || !aligned16(g.B[s])) return TB200_ERR_INVALID;
+    p.src_n[s] = g.N[s];
+    p.src_tile0[s] = tiles;
+    if (g.mode == GEMM_SWIGLU) {
+      if (s == 0) tiles += (g.N[0] + 127) / 128;
+    } else {
+      tiles += (g.N[s] + BN - 1) / BN;
+    }
+  }
+  if (g.mode == GEMM_SWIGLU && (g.n_src != 2 || g.N[0] != g.N[1])) return TB200_ERR_INVALID;
+  if (g.mode == GEMM_QKV) {
+    if (g.n_src != 3 || (g.D != 64 && g.D != 128) || g.S <= 0 || g.M % g.S != 0) return TB200_ERR_INVALID;
+    if (g.N[0] != g.Hq * g.D || g.N[1] != g.Hkv * g.D || g.N[2] != g.Hkv * g.D) return TB200_ERR_INVALID;
+    if (g.q_out == nullptr || g.k_cache == nullptr || g.v_cache == nullptr || g.past < 0 || g.cache_len < g.past + g.S)
+      return TB200_ERR_INVALID;
+    if (!aligned16(g.q_out) || !aligned16(g.k_cache) || !aligned16(g.v_cache)) return TB200_ERR_INVALID;
+  }
+  if (g.mode == GEMM_STORE || g.mode == GEMM_SWIGLU) {
+    if (g.C == nullptr || !aligned16(g.C) || (g.ldc & 7) != 0 || !aligned16(g.residual) || (g.ldr & 7) != 0) return TB200_ERR_INVALID;
+  }
+  if (g.mode == GEMM_PARTIAL && (g.partial == nullptr || !aligned16(g.partial))) return TB200_ERR_INVALID;
+  for (int s = g.n_src; s < 4; ++s) p.src_tile0[s] = tiles;
+  p.src_tile0[g.n_src] = tiles;
+  p.n_tiles = tiles;
+  const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.split_k;
+  if (units > 0x7fffffffLL) return TB200_ERR_INVALID;
+  p.total_units = static_cast<int>(units);
+  p.err = st->err_word;
+  p.row_scale = g.row_scale;
+  p.C = g.C;
+  p.ldc = g.ldc;
+  p.residual = g.residual;
+  p.ldr = g.ldr;
+  p.C2 = g.C2;
+  p.act = g.act;
+  p.q_out = g.q_out;
+  p.k_cache = g.k_cache;
+  p.v_cache = g.v_cache;
+  p.S = g.S; p.Hq = g.Hq; p.Hkv = g.Hkv; p.D = g.D; p.past = g.past; p.cache_len = g.cache_len;
+  p.qknorm = g.qknorm;
+  p.qk_eps = g.qk_eps;
+  p.q_norm_weight = g.q_norm_weight;
+  p.k_norm_weight = g.k_norm_weight;
+  p.partial = g.partial;
+  long long ldp = 0;
+  for (int s = 0; s < g.n_src; ++s) ldp += g.N[s];
+  p.ldp = ldp;
+
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(g.K) * 2};
+    const uint32_t box[2] = {BK, BM};
+    if ((status = make_tensor_map(&p.map_a, g.A, 2, dims, strides, box)) != TB200_OK) return status;
+  }
+  for (int s = 0; s < g.n_src; ++s) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(g.N[s]), static_cast<uint64_t>(g.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(g.N[s]) * 2};
+    const uint32_t box[2] = {64, BK};
+    if ((status = make_tensor_map(&p.map_b[s], g.B[s], 2, dims, strides, box)) != TB200_OK) return status;
+  }
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  if (g.dtype == TB200_BF16) return launch_typed<__nv_bfloat16>(p, g.mode, grid, stream);
+  return launch_typed<__half>(p, g.mode, grid, stream);
+}
+
+int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
+  if (f.M <= 0 || f.N <= 0 || (f.N & 7) != 0 || f.partial == nullptr || f.C == nullptr) return TB200_ERR_INVALID;
+  const int64_t total = static_cast<int64_t>(f.M) * (f.N / 8);
+  const int threads = 256;
+  int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (f.dtype == TB200_BF16) {
+    splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
+  } else if (f.dtype == TB200_F16) {
+    splitk_finish_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
+  } else {
+    return TB200_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
+
+}  // namespace tb200

@@ -1,0 +1,134 @@
+// Host-side declarations shared by the translation units of libtrinity_b200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/trinity_b200.h"
+
+namespace tb200 {
+
+// Per-device state created by the first call on that device (outside any stream capture):
+// the device error word, the SM count and opt-in shared-memory attributes of the kernels.
+struct DeviceState {
+  int device = -1;
+  int num_sms = 0;
+  int* err_word = nullptr;  // device memory, 4 bytes, zero when healthy
+};
+// Returns nullptr (and sets *status) if the state cannot be created.
+DeviceState* device_state(int* status);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
+// 2D/3D row-major tensors of 16-bit elements, 128-byte swizzle, zero fill outside the bounds.
+//   dims[0] is the contiguous (inner) extent in elements; strides_bytes[i] is the pitch of dims[i+1].
+int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---------------------------------------------------------------- rmsnorm.cu
+// mean_divisor: the sum of squares is divided by this instead of cols when > 0 (the reference's Falcon
+// tail hard-codes 4544, baseline/ffn_ref.py:121).
+int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
+                   float eps, int dtype, cudaStream_t stream, int mean_divisor = 0);
+
+// ---------------------------------------------------------------- gemm.cu
+enum GemmMode {
+  GEMM_STORE = 0,    // c = act(acc * row_scale) + residual
+  GEMM_SWIGLU = 1,   // two B sources of equal width: c = silu(acc0 * rs) * (acc1 * rs)
+  GEMM_QKV = 2,      // three B sources (Wq, Wk, Wv): head split, optional per-head RMSNorm, cache append
+  GEMM_PARTIAL = 3   // fp32 partial sums of one K slice into the workspace
+};
+struct GemmLaunch {
+  int dtype = TB200_BF16;
+  int mode = GEMM_STORE;
+  int M = 0, K = 0;
+  const void* A = nullptr;          // (M,K), pitch K
+  int n_src = 1;
+  const void* B[3] = {nullptr, nullptr, nullptr};  // (K, N[i]), pitch N[i]
+  int N[3] = {0, 0, 0};
+  const float* row_scale = nullptr;
+  // GEMM_STORE / GEMM_SWIGLU
+  void* C = nullptr;
+  int64_t ldc = 0;
+  const void* residual = nullptr;
+  int64_t ldr = 0;
+  void* C2 = nullptr;               // optional: the value before the residual is added (pitch ldc)
+  int act = 0;
+  // GEMM_QKV
+  void* q_out = nullptr;            // (B,Hq,S,D)
+  void* k_cache = nullptr;          // (B,Hkv,cache_len,D)
+  void* v_cache = nullptr;
+  int S = 0, Hq = 0, Hkv = 0, D = 0, past = 0, cache_len = 0;
+  int qknorm = 0;
+  float qk_eps = 0.f;
+  const void* q_norm_weight = nullptr;
+  const void* k_norm_weight = nullptr;
+  // GEMM_PARTIAL
+  int split_k = 1;
+  float* partial = nullptr;         // (split_k, M, sum N[i])
+};
+int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+
+// Sum the K slices and apply the epilogue: out = act(sum * row_scale) [silu-gated by the second half] + residual.
+struct SplitKFinish {
+  int dtype = TB200_BF16;
+  int M = 0, N = 0;                 // N = output width
+  int split_k = 1;
+  const float* partial = nullptr;   // (split_k, M, ldp)
+  int64_t ldp = 0;                  // N, or 2N when gated
+  int gated = 0;                    // columns [0,N) = gate, [N,2N) = up
+  int act = 0;
+  const float* row_scale = nullptr;
+  const void* residual = nullptr;
+  int64_t ldr = 0;
+  void* C = nullptr;
+  int64_t ldc = 0;
+  void* C2 = nullptr;               // optional: the value before the residual is added
+};
+int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream);
+
+// ---------------------------------------------------------------- attn.cu
+struct AttnLaunch {
+  int dtype = TB200_BF16;
+  int B = 0, S = 0, Hq = 0, Hkv = 0, D = 0, past = 0, cache_len = 0;
+  int causal = 0;
+  float sm_scale = 1.f;
+  const void* q = nullptr;          // (B,Hq,S,D)
+  const void* k_cache = nullptr;    // (B,Hkv,cache_len,D)
+  const void* v_cache = nullptr;
+  void* o2 = nullptr;               // (B,S,Hq*D)
+  float* lse2 = nullptr;            // (B,Hq,S): log2-domain log-sum-exp of scale*s
+  // KeyFormer: second statistic over (scale*s + noise)/tau
+  const void* noise = nullptr;      // (B,Hq,S,past+S)
+  float tau = 1.f;
+  float* lse2_perturbed = nullptr;  // (B,Hq,S)
+};
+int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream);
+
+// ---------------------------------------------------------------- score.cu
+struct ScoreLaunch {
+  int dtype = TB200_BF16;
+  int B = 0, S = 0, Hq = 0, Hkv = 0, D = 0, past = 0, cache_len = 0;
+  int causal = 0;
+  float sm_scale = 1.f;
+  const void* q = nullptr;
+  const void* k_cache = nullptr;
+  const float* lse2 = nullptr;
+  const void* noise = nullptr;      // KeyFormer
+  float tau = 1.f;
+  const float* lse2_perturbed = nullptr;
+  float* sum_p = nullptr;           // (B,Hq,past+S) or NULL
+  float* sum_p2 = nullptr;
+  float* sum_pt = nullptr;          // KeyFormer
+};
+int launch_score_colreduce(const ScoreLaunch& s, cudaStream_t stream);
+
+// ---------------------------------------------------------------- topk.cu / misc
+int launch_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, cudaStream_t stream);
+int launch_cast_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t stream);
+
+}  // namespace tb200

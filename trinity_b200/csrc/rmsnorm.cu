@@ -1,0 +1,120 @@
+// RMSNorm / row statistics: the bandwidth-bound kernel class.
+// One CTA per row; 128-bit coalesced loads, the row is kept in registers between the
+// sum-of-squares pass and the scale pass (one HBM read, one HBM write per element),
+// warp-shuffle + one shared-memory hop for the reduction, fp32 accumulation.
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCachedVecs = 4;  // 16-byte vectors a thread keeps in registers: rows up to 256*4*8 = 8192 elements
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ weight,
+                                                         T* __restrict__ y, float* __restrict__ inv_rms, int cols,
+                                                         float eps, float divisor) {
+  const int64_t row = blockIdx.x;
+  const int nvec = cols >> 3;  // 8 elements per 16-byte vector
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  uint4 cache[kCachedVecs];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kCachedVecs; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) {
+      cache[i] = __ldg(xr + v);
+      const uint32_t w[4] = {cache[i].x, cache[i].y, cache[i].z, cache[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Pack2<T>::unpack(w[j]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+  }
+  for (int v = threadIdx.x + kCachedVecs * kThreads; v < nvec; v += kThreads) {  // rows wider than the register cache
+    const uint4 u = __ldg(xr + v);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = Pack2<T>::unpack(w[j]);
+      ss = fmaf(f.x, f.x, ss);
+      ss = fmaf(f.y, f.y, ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __shared__ float warp_sums[kThreads / 32];
+  if (lane_id() == 0) warp_sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) total += warp_sums[i];  // same order in every thread: deterministic
+  const float r = rsqrtf(total / divisor + eps);
+  if (inv_rms != nullptr && threadIdx.x == 0) inv_rms[row] = r;
+  if (y == nullptr) return;
+
+  uint4* yr = reinterpret_cast<uint4*>(y + row * cols);
+  const uint4* wr = reinterpret_cast<const uint4*>(weight);
+  auto scale_store = [&](int v, const uint4& u) {
+    const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+    uint32_t out[4];
+    uint4 g = make_uint4(0, 0, 0, 0);
+    if (wr != nullptr) g = __ldg(wr + v);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = Pack2<T>::unpack(in[j]);
+      f.x *= r;
+      f.y *= r;
+      if (wr != nullptr) {
+        const float2 gf = Pack2<T>::unpack(gw[j]);
+        f.x *= gf.x;
+        f.y *= gf.y;
+      }
+      out[j] = Pack2<T>::pack(f.x, f.y);
+    }
+    yr[v] = make_uint4(out[0], out[1], out[2], out[3]);
+  };
+#pragma unroll
+  for (int i = 0; i < kCachedVecs; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) scale_store(v, cache[i]);
+  }
+  for (int v = threadIdx.x + kCachedVecs * kThreads; v < nvec; v += kThreads) scale_store(v, __ldg(xr + v));
+}
+
+}  // namespace
+
+int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols, float eps,
+                   int dtype, cudaStream_t stream, int mean_divisor) {
+  if (x == nullptr || (y == nullptr && inv_rms == nullptr)) return TB200_ERR_INVALID;
+  if (rows < 0 || cols <= 0 || (cols & 7) != 0 || rows > 0x7fffffffLL || cols > (1 << 24)) return TB200_ERR_INVALID;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(weight)) return TB200_ERR_INVALID;
+  if (rows == 0) return TB200_OK;
+  const dim3 grid(static_cast<unsigned>(rows));
+  const float divisor = static_cast<float>(mean_divisor > 0 ? mean_divisor : cols);
+  if (dtype == TB200_BF16) {
+    rmsnorm_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                              static_cast<const __nv_bfloat16*>(weight),
+                                                              static_cast<__nv_bfloat16*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
+  } else if (dtype == TB200_F16) {
+    rmsnorm_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(weight),
+                                                       static_cast<__half*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
+  } else {
+    return TB200_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
+
+}  // namespace tb200
+
+extern "C" int tb200_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
+                             float eps, int dtype, void* stream) {
+  int status = TB200_OK;
+  if (tb200::device_state(&status) == nullptr) return status;
+  return tb200::launch_rmsnorm(x, weight, y, inv_rms, rows, cols, eps, dtype, static_cast<cudaStream_t>(stream));
+}

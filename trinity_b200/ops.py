@@ -1,0 +1,149 @@
+"""Tensor-level wrappers over the C ABI: torch tensors in, raw device pointers across the boundary.
+
+PyTorch is plumbing here (device memory, streams); every operator below runs in libtrinity_b200.so.
+All wrappers launch on ``torch.cuda.current_stream()`` and allocate nothing once their workspace has
+been cached, so they can be captured in a CUDA graph after one warm-up call.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib as L
+
+_DT = {torch.float16: L.F16, torch.bfloat16: L.BF16, torch.float32: L.F32}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("trinity_b200 operators take CUDA tensors (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("trinity_b200 operators take contiguous tensors")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Workspace:
+    """A grow-only device buffer per (device, tag); grown outside of graph capture by the first call."""
+
+    _bufs: Dict[tuple, torch.Tensor] = {}
+
+    @classmethod
+    def get(cls, device: torch.device, nbytes: int, tag: str = "default") -> Optional[torch.Tensor]:
+        if nbytes == 0:
+            return None
+        key = (device.index, tag)
+        buf = cls._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("workspace must be sized by one call outside CUDA-graph capture first")
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            cls._bufs[key] = buf
+        return buf
+
+
+def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+            out: Optional[torch.Tensor] = None, inv_rms: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = L.load()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty_like(x)
+    L.check(lib.tb200_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), _ptr(inv_rms), rows, cols, eps, _dt(x), _stream()), "tb200_rmsnorm")
+    return out
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, b2: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, act: int = 0, split_k: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = L.load()
+    m, k = a.shape
+    n = b.shape[1]
+    if out is None:
+        out = torch.empty(m, n, dtype=a.dtype, device=a.device)
+    args = L.GemmArgs(dtype=_dt(a), act=act, m=m, n=n, k=k, a=_ptr(a), b=_ptr(b), b2=_ptr(b2), c=_ptr(out),
+                      row_scale=_ptr(row_scale), residual=_ptr(residual), split_k=split_k)
+    need = lib.tb200_gemm_workspace_bytes(C.byref(args))
+    ws = Workspace.get(a.device, need, "gemm")
+    args.workspace, args.workspace_bytes = _ptr(ws), need
+    L.check(lib.tb200_gemm(C.byref(args), _stream()), "tb200_gemm")
+    return out
+
+
+def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: int, flags: int = 0,
+                 sm_scale: float = 1.0, norm_weight=None, norm_eps: float = 0.0, q_norm_weight=None,
+                 k_norm_weight=None, qk_eps: float = 0.0, noise=None, tau: float = 1.5, c_out=None,
+                 c_out1=None, c_out2=None, topk: int = 0, topk_idx=None) -> None:
+    """The fused attention block; mutates ``o2``, the cache rows ``[past, past+S)`` and the c_out* tensors."""
+    lib = L.load()
+    if x.dim() == 2:
+        batch, (seq, hidden) = 1, x.shape
+    else:
+        batch, seq, hidden = x.shape
+    n_q = wq.shape[1] // head_dim
+    n_kv = wk.shape[1] // head_dim
+    cache_len = k_cache.shape[-2]
+    aux = c_out if c_out is not None else c_out1
+    args = L.AttnArgs(
+        dtype=_dt(x), flags=flags, batch=batch, seq=seq, hidden=hidden, n_q_heads=n_q, n_kv_heads=n_kv,
+        head_dim=head_dim, past=past, cache_len=cache_len, sm_scale=sm_scale, norm_eps=norm_eps, qk_eps=qk_eps, tau=tau,
+        x=_ptr(x), wq=_ptr(wq), wk=_ptr(wk), wv=_ptr(wv), k_cache=_ptr(k_cache), v_cache=_ptr(v_cache), o2=_ptr(o2),
+        norm_weight=_ptr(norm_weight), q_norm_weight=_ptr(q_norm_weight), k_norm_weight=_ptr(k_norm_weight),
+        noise=_ptr(noise), c_out=_ptr(c_out), c_out1=_ptr(c_out1), c_out2=_ptr(c_out2),
+        aux_dtype=_dt(aux) if aux is not None else L.F32, topk=topk, topk_idx=_ptr(topk_idx))
+    need = lib.tb200_attn_workspace_bytes(C.byref(args))
+    if need == 0:
+        raise L.Tb200Error(-1, "tb200_attn_workspace_bytes")
+    ws = Workspace.get(x.device, need, "attn")
+    args.workspace, args.workspace_bytes = _ptr(ws), need
+    L.check(lib.tb200_attn_forward(C.byref(args), _stream()), "tb200_attn_forward")
+
+
+def ffn_forward(x, w_gate, w_up, w_down, ff2, *, act: int = L.FFN_SWIGLU, flags: int = 0, o2=None, wo=None,
+                norm_weight=None, norm_eps: float = 0.0, tail_divisor: int = 0, attn_o2=None, ff1=None,
+                o_ff_norm=None) -> None:
+    """The fused FFN block; mutates ``ff2`` (and ``attn_o2`` / ``ff1`` / ``o_ff_norm`` when given)."""
+    lib = L.load()
+    hidden = x.shape[-1]
+    tokens = x.numel() // hidden
+    inner = w_gate.shape[1]
+    args = L.FfnArgs(dtype=_dt(x), act=act, flags=flags, tokens=tokens, hidden=hidden, inner=inner, norm_eps=norm_eps,
+                     tail_divisor=tail_divisor, x=_ptr(x), o2=_ptr(o2), wo=_ptr(wo), norm_weight=_ptr(norm_weight),
+                     w_gate=_ptr(w_gate), w_up=_ptr(w_up), w_down=_ptr(w_down), ff2=_ptr(ff2), attn_o2=_ptr(attn_o2),
+                     ff1=_ptr(ff1), o_ff_norm=_ptr(o_ff_norm))
+    need = lib.tb200_ffn_workspace_bytes(C.byref(args))
+    ws = Workspace.get(x.device, need, "ffn")
+    args.workspace, args.workspace_bytes = _ptr(ws), need
+    L.check(lib.tb200_ffn_forward(C.byref(args), _stream()), "tb200_ffn_forward")
+
+
+def topk(scores: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = L.load()
+    n = scores.shape[-1]
+    rows = scores.numel() // n
+    if out is None:
+        out = torch.empty(*scores.shape[:-1], k, dtype=torch.int32, device=scores.device)
+    L.check(lib.tb200_topk(_ptr(scores), _ptr(out), rows, n, k, _stream()), "tb200_topk")
+    return out
+
+
+def device_status() -> int:
+    """Synchronise and return the device error word (0 = healthy); raises on a recorded timeout."""
+    code = C.c_int(0)
+    status = L.load().tb200_device_status(C.byref(code))
+    if status != 0:
+        raise L.Tb200Error(status, f"tb200_device_status (device code {code.value})")
+    return code.value
