@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the fused attention block on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Workload (default): Llama-3-8B Vanilla attention block, prefill -- batch 8, seq 2048, hidden 4096,
+GQA 32/8 heads, head_dim 128, causal, scale 1/sqrt(128), bf16; synthetic seeded inputs (x ~ N(0,1),
+weights ~ N(0,0.02)).  One step = one forward of the block (QKV projection + cache append + causal
+attention) over one batch.  At N GPUs every rank runs its own batch (batch-sharded, no collective).
+
+Prints ONE JSON line.  `value` is TFLOP/s from the algorithmic FLOPs of the block
+(2*T*N*(Hq+2Hkv)*D for the projection + 4*B*Hq*S^2*D/2 for causal attention) with inputs resident in
+HBM; `e2e` is the same through the generated-module forward() with pinned HOST buffers copied in and the
+result copied out inside the timed region.  `--impl reference` times the CPU oracle (the fp32
+restatement of the reference's eager PyTorch classes) on the host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: B, S, N, Hq, Hkv, D, variant
+    "llama3_8b_vanilla_prefill_b8_s2048": dict(B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),
+    "llama3_8b_qknorm_prefill_b8_s2048": dict(B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="qknorm"),
+    "llama3_8b_prenorm_b8_s4096": dict(B=8, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="prenorm"),
+    "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
+    "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
+}
+DEFAULT = "llama3_8b_vanilla_prefill_b8_s2048"
+
+
+def block_flops(w, batch=None):
+    B = w["B"] if batch is None else batch
+    T = B * w["S"]
+    proj = 2.0 * T * w["N"] * (w["Hq"] + 2 * w["Hkv"]) * w["D"]
+    attn = 4.0 * B * w["Hq"] * w["S"] * w["S"] * w["D"] / 2.0
+    return proj, attn
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            if len(s) < 6:
+                continue
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def make_inputs(w, dtype, seed):
+    from oracle import oracle as orc
+    t = orc.bench_attention_inputs(w["B"], w["S"], w["N"], w["Hq"], w["Hkv"], w["D"], seed=seed,
+                                   norm_weights=w["variant"] in ("qknorm", "prenorm"))
+    return {k: v.to(dtype) for k, v in t.items()}
+
+
+def oracle_step(w, t, batch_slice):
+    """The CPU oracle on `batch_slice` sequences of the workload (fp32, all host threads)."""
+    from oracle import oracle as orc
+    B = batch_slice
+    x = t["X"][:B].float()
+    kc = torch.zeros(B, w["Hkv"], w["S"], w["D"])
+    vc = torch.zeros(B, w["Hkv"], w["S"], w["D"])
+    kw = {}
+    if w["variant"] == "qknorm":
+        kw = dict(qknorm=True, q_norm_weight=t["q_norm_weight"].float(), k_norm_weight=t["k_norm_weight"].float(), qk_eps=1e-6)
+    if w["variant"] == "prenorm":
+        kw = dict(prenorm=True, norm_weight=t["norm_weight"].float(), norm_eps=1e-5)
+    return orc.attention_block(x, t["WQ"].float(), t["WK"].float(), t["WV"].float(), kc, vc, past=0, head_dim=w["D"],
+                               causal=True, sm_scale=w["D"] ** -0.5, **kw)
+
+
+def time_cpu(w, t, steps, warmup, batch_slice):
+    torch.set_num_threads(os.cpu_count())
+    for _ in range(warmup):
+        oracle_step(w, t, batch_slice)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle_step(w, t, batch_slice)
+    dt = (time.perf_counter() - t0) / steps
+    proj, attn = block_flops(w, batch_slice)
+    return dt, (proj + attn) / dt / 1e12
+
+
+def run_reference(args, w, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t = make_inputs(w, torch.float32, seed=0)
+    dt, tflops = time_cpu(w, t, args.steps, min(args.warmup, 1), batch_slice=1)
+    cores = os.cpu_count()
+    line = {
+        "impl": "reference", "metric": "fused_block_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "sample": "1 sequence (batch 1) of the workload per step"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "1 sequence (batch 1, seq %d) per step, fp32 oracle port of the reference's eager classes" % w["S"]},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, w, args.workload)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: trinity_b200 has no CPU path (use --impl reference for the CPU oracle)")
+    import torch.distributed as dist
+    from trinity_b200 import _lib as L
+    from trinity_b200 import ops
+    from trinity_b200.codegen import convert_ir_to_triton
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dtype = torch.bfloat16
+    host = make_inputs(w, dtype, seed=rank)          # every rank its own batch
+    B, S, N, Hq, Hkv, D = (w[k] for k in ("B", "S", "N", "Hq", "Hkv", "D"))
+    flags = L.ATTN_CAUSAL | {"vanilla": 0, "qknorm": L.ATTN_QKNORM, "prenorm": L.ATTN_PRENORM}[w["variant"]]
+    x = host["X"].to(dev)
+    wq, wk, wv = host["WQ"].to(dev), host["WK"].to(dev), host["WV"].to(dev)
+    nw = host.get("norm_weight")
+    qw, kw_ = host.get("q_norm_weight"), host.get("k_norm_weight")
+    nw, qw, kw_ = (None if v is None else v.to(dev) for v in (nw, qw, kw_))
+    k_cache = torch.zeros(B, Hkv, S, D, dtype=dtype, device=dev)
+    v_cache = torch.zeros(B, Hkv, S, D, dtype=dtype, device=dev)
+    o2 = torch.zeros(B, S, Hq * D, dtype=dtype, device=dev)
+    kwargs = dict(past=0, head_dim=D, flags=flags, sm_scale=D ** -0.5, norm_weight=nw if flags & L.ATTN_PRENORM else None,
+                  norm_eps=1e-5, q_norm_weight=qw if flags & L.ATTN_QKNORM else None,
+                  k_norm_weight=kw_ if flags & L.ATTN_QKNORM else None, qk_eps=1e-6)
+
+    def step():
+        ops.attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, **kwargs)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    ops.device_status()
+
+    # ---- device-resident timing: K steps between CUDA events on the launching stream
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+
+    # ---- per-stage times (CUDA events between the stages, same stream, same inputs)
+    stage = [0.0, 0.0, 0.0, 0.0]
+    for _ in range(args.steps):
+        s_ms = ops.attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, timed=True, **kwargs)
+        stage = [a + b / args.steps for a, b in zip(stage, s_ms)]
+
+    # ---- end to end through the generated module: pinned host X in, O2 out, every step
+    ir_text = "(ploop 0 %d %d n (seq (store (input K_cache,V_cache) (load (input X) (index fulltile)) (index fulltile)) " \
+              "(store (output O2) (* (load (input X) (index fulltile)) (load (input WQ,WK,WV) (index fulltile))) (index fulltile))))" % (N, D)
+    constants = {"M": S, "D": D, "N": N, "P": 0, "H": Hq, "H_KV": Hkv, "CAUSAL": 1, "SM_SCALE": D ** -0.5,
+                 "NORM_EPS": 1e-5, "QK_EPS": 1e-6}
+    if w["variant"] == "vanilla":
+        src = convert_ir_to_triton(ir_text, None, constants)
+        ns = {}
+        exec(compile(src, "<generated module>", "exec"), ns)
+        forward, params = ns["forward"], ns["TENSOR_PARAMS"]
+        named = {"K_cache": k_cache, "O2": o2, "V_cache": v_cache, "WK": wk, "WQ": wq, "WV": wv, "X": x}
+
+        def api_step():
+            forward(*[named[p] for p in params])
+    else:
+        api_step = step
+    x_host = host["X"].pin_memory()
+    o_host = torch.empty(B, S, Hq * D, dtype=dtype).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        api_step()
+        o_host.copy_(o2, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    ops.device_status()
+
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+
+    proj, attn = block_flops(w)
+    total = (proj + attn) * world
+    peaks = load_peaks()
+    if rank == 0:
+        gemm_tflops = proj / (stage[1] * 1e-3) / 1e12 if stage[1] > 0 else None
+        attn_tflops = attn / (stage[2] * 1e-3) / 1e12 if stage[2] > 0 else None
+        peak = peaks["bf16_tflops"]
+        line = {
+            "metric": "fused_block_tflops", "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "us_per_call": ms * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "seq_len": S, "hidden": N, "q_heads": Hq, "kv_heads": Hkv,
+                       "head_dim": D, "causal": True, "parallelism": f"batch-sharded x{world}, no collective",
+                       "l2": "working set (x, weights, q, caches, o2 > 400 MB) exceeds the 126 MB L2"},
+            "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
+                    "api": "generated-module forward(*TENSOR_PARAMS)"},
+            "gpu_launches": args.steps * (2 + (1 if flags & L.ATTN_PRENORM else 0)),
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<bf16, QKV> (tcgen05 QKV projection)",
+                         "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
+                         "frac": (gemm_tflops / peak) if gemm_tflops else None, "peak_source": peaks["source"] + " burst cuBLAS bf16",
+                         "traffic": None, "flops_per_launch": proj, "ms_per_launch": stage[1]},
+            "stages": {"rmsnorm_ms": stage[0], "qkv_gemm_ms": stage[1], "attention_ms": stage[2], "scores_ms": stage[3],
+                       "qkv_gemm_tflops": gemm_tflops, "attention_tflops": attn_tflops,
+                       "attention_frac_of_peak": (attn_tflops / peak) if attn_tflops else None},
+            "block_frac_of_peak": total / world / (ms * 1e-3) / 1e12 / peak,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            cpu_t = {k: v.float() for k, v in host.items()}
+            dt, tf = time_cpu(w, cpu_t, steps=1, warmup=0, batch_slice=1)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "seconds": dt,
+                                    "sample": "1 of %d sequences (seq %d), 1 timed pass, fp32 oracle port of the reference's eager classes" % (B, S)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -122,6 +122,12 @@ typedef struct {
 } tb200_attn_args;
 size_t tb200_attn_workspace_bytes(const tb200_attn_args* args);
 int tb200_attn_forward(const tb200_attn_args* args, void* stream);
+/* Measuring aid with no counterpart in the reference (its harness times whole forward() calls,
+ * benchmark/vanilla_llama_benchmark.py:277-294): the same block, with CUDA events recorded on `stream`
+ * between its stages; waits for the stream and returns the stage durations in milliseconds:
+ * [0] RMSNorm prologue, [1] QKV projection, [2] attention, [3] per-key reductions + top-k.
+ * Creates and destroys events: not for use under graph capture. */
+int tb200_attn_forward_timed(const tb200_attn_args* args, void* stream, float* stage_ms);
 
 /* ---------------------------------------------------------------------------------------------
  * Fused FFN block -- replaces kernel_0..2 of evaluation/ffn/ffn_llama/ffn_llama_benchmark2248.py:19-258

@@ -114,7 +114,7 @@ def main():
     torch.set_num_threads(os.cpu_count())
 
     # ---- small, self-contained ----
-    for tag, (M, N, D, P) in {"a": (16, 128, 32, 48), "b": (8, 256, 128, 0), "c": (5, 192, 64, 33)}.items():
+    for tag, (M, N, D, P) in {"a": (16, 128, 64, 48), "b": (8, 256, 128, 0), "c": (5, 192, 64, 33)}.items():
         inp = orc.ref_attention_inputs(M, N, D, P, seed=42, std=0.2)
         blob = {"shape": np.asarray([M, N, D, P])}
         blob.update({"in_" + k: v.numpy() for k, v in inp.items()})

@@ -1,0 +1,56 @@
+"""Helpers shared by the GPU parity tests: run a fused block through the C ABI and through the oracle
+on the same seeded, dtype-rounded inputs."""
+import torch
+
+from oracle import oracle as orc
+from trinity_b200 import _lib as L
+from trinity_b200 import ops
+
+RTOL = ATOL = 2e-2     # 16-bit kernels against the fp32 oracle
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def close(got, ref, rtol=RTOL, atol=ATOL, msg=""):
+    torch.testing.assert_close(got.float().cpu(), ref.float().cpu(), rtol=rtol, atol=atol, msg=lambda m: f"{msg}: {m}")
+
+
+def attention_case(B, S, N, Hq, Hkv, D, P, flags, dt=torch.bfloat16, scale=None, weights=False, topk=0, tau=1.0,
+                   seed=1, aux_dtype=torch.float32, cache_extra=0):
+    """Returns (gpu outputs dict, oracle outputs dict)."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    x = rn(B, S, N)
+    wq, wk, wv = rn(N, Hq * D) * N ** -0.5, rn(N, Hkv * D) * N ** -0.5, rn(N, Hkv * D) * N ** -0.5
+    kc, vc = rn(B, Hkv, P + S + cache_extra, D), rn(B, Hkv, P + S + cache_extra, D)
+    nw = (1 + 0.02 * rn(N)) if weights else None
+    qw = (1 + 0.02 * rn(D)) if weights else None
+    kw = (1 + 0.02 * rn(D)) if weights else None
+    noise = orc.gumbel_noise((B, Hq, S, P + S), g) if flags & L.ATTN_KEYFORMER else None
+    scale = D ** -0.5 if scale is None else scale
+    cast = lambda t: None if t is None else t.to(dt)
+    xs, wqs, wks, wvs, kcs, vcs, nws, qws, kws, ns = map(cast, (x, wq, wk, wv, kc, vc, nw, qw, kw, noise))
+    f32 = lambda t: None if t is None else t.float()
+    ref = orc.attention_block(
+        f32(xs), f32(wqs), f32(wks), f32(wvs), f32(kcs), f32(vcs), past=P, head_dim=D,
+        prenorm=bool(flags & L.ATTN_PRENORM), norm_weight=f32(nws), norm_eps=1e-5 if weights else 0.0,
+        qknorm=bool(flags & L.ATTN_QKNORM), q_norm_weight=f32(qws), k_norm_weight=f32(kws), qk_eps=1e-6 if weights else 0.0,
+        causal=bool(flags & L.ATTN_CAUSAL), sm_scale=scale, noise=f32(ns), tau=tau, roco=bool(flags & L.ATTN_ROCO), topk=topk)
+    d = lambda t: None if t is None else t.to(dev())
+    kcd, vcd = d(kcs), d(vcs)
+    o2 = torch.full((B, S, Hq * D), float("nan"), dtype=dt, device=dev())     # poison: the kernel must overwrite
+    Lk = P + S
+    mk = lambda: torch.full((B, Hq, Lk), float("nan"), dtype=aux_dtype, device=dev())
+    c_out = mk() if flags & L.ATTN_KEYFORMER else None
+    c1 = mk() if flags & L.ATTN_ROCO else None
+    c2 = mk() if flags & L.ATTN_ROCO else None
+    ti = torch.full((B, Hq, topk), -1, dtype=torch.int32, device=dev()) if topk else None
+    ops.attn_forward(d(xs), d(wqs), d(wks), d(wvs), kcd, vcd, o2, past=P, head_dim=D, flags=flags, sm_scale=scale,
+                     norm_weight=d(nws), norm_eps=1e-5 if weights else 0.0, q_norm_weight=d(qws), k_norm_weight=d(kws),
+                     qk_eps=1e-6 if weights else 0.0, noise=d(ns), tau=tau, c_out=c_out, c_out1=c1, c_out2=c2, topk=topk, topk_idx=ti)
+    ops.device_status()
+    got = {"O2": o2, "K_new": kcd[:, :, P:P + S], "V_new": vcd[:, :, P:P + S], "K_cache": kcd, "V_cache": vcd,
+           "K_cache_in": kcs, "V_cache_in": vcs, "C_out": c_out, "C_out1": c1, "C_out2": c2, "topk_idx": ti}
+    return got, ref

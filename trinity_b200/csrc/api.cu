@@ -199,7 +199,8 @@ size_t tb200_attn_workspace_bytes(const tb200_attn_args* a) {
   return carve_attn(a, nullptr).bytes;
 }
 
-int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
+// ev: null, or 5 events recorded on the stream at the stage boundaries
+static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_t* ev) {
   int status = TB200_OK;
   DeviceState* st = device_state(&status);
   if (!st) return status;
@@ -215,6 +216,7 @@ int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
   //    row statistic is computed and the scale is applied in the projection's epilogue.
   const void* A = a->x;
   const float* row_scale = nullptr;
+  if (ev) cudaEventRecord(ev[0], stream);
   if (a->flags & TB200_ATTN_PRENORM) {
     if (a->norm_weight) {
       status = launch_rmsnorm(a->x, a->norm_weight, w.x_norm, nullptr, T, a->hidden, a->norm_eps, a->dtype, stream);
@@ -226,6 +228,7 @@ int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
     if (status != TB200_OK) return status;
   }
   // 2. QKV projection with head split, optional per-head norm and cache append in the epilogue.
+  if (ev) cudaEventRecord(ev[1], stream);
   {
     GemmLaunch g;
     g.dtype = a->dtype;
@@ -245,6 +248,7 @@ int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
     if ((status = launch_gemm(g, stream)) != TB200_OK) return status;
   }
   // 3. softmax(QK^T)V
+  if (ev) cudaEventRecord(ev[2], stream);
   {
     AttnLaunch f;
     f.dtype = a->dtype;
@@ -261,6 +265,7 @@ int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
     if ((status = launch_attn_fwd(f, stream)) != TB200_OK) return status;
   }
   // 4. per-key reductions (second pass) and top-k
+  if (ev) cudaEventRecord(ev[3], stream);
   if (a->flags & (TB200_ATTN_KEYFORMER | TB200_ATTN_ROCO)) {
     const bool kf = a->flags & TB200_ATTN_KEYFORMER, rc = a->flags & TB200_ATTN_ROCO;
     const bool stage = a->aux_dtype != TB200_F32;
@@ -298,7 +303,25 @@ int tb200_attn_forward(const tb200_attn_args* a, void* stream_) {
       if (status != TB200_OK) return status;
     }
   }
+  if (ev) cudaEventRecord(ev[4], stream);
   return TB200_OK;
+}
+
+int tb200_attn_forward(const tb200_attn_args* a, void* stream) { return attn_forward_impl(a, stream, nullptr); }
+
+int tb200_attn_forward_timed(const tb200_attn_args* a, void* stream, float* stage_ms) {
+  if (stage_ms == nullptr) return TB200_ERR_INVALID;
+  cudaEvent_t ev[5];
+  for (int i = 0; i < 5; ++i)
+    if (cudaEventCreate(&ev[i]) != cudaSuccess) return TB200_ERR_CUDA;
+  int status = attn_forward_impl(a, stream, ev);
+  if (status == TB200_OK && cudaEventSynchronize(ev[4]) != cudaSuccess) status = TB200_ERR_CUDA;
+  for (int i = 0; i < 4; ++i) {
+    stage_ms[i] = 0.f;
+    if (status == TB200_OK && cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]) != cudaSuccess) status = TB200_ERR_CUDA;
+  }
+  for (int i = 0; i < 5; ++i) cudaEventDestroy(ev[i]);
+  return status;
 }
 
 // ----------------------------------------------------------------------------------------- FFN

@@ -86,8 +86,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, b2: Optional[torch.Tensor] = None,
 def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: int, flags: int = 0,
                  sm_scale: float = 1.0, norm_weight=None, norm_eps: float = 0.0, q_norm_weight=None,
                  k_norm_weight=None, qk_eps: float = 0.0, noise=None, tau: float = 1.5, c_out=None,
-                 c_out1=None, c_out2=None, topk: int = 0, topk_idx=None) -> None:
-    """The fused attention block; mutates ``o2``, the cache rows ``[past, past+S)`` and the c_out* tensors."""
+                 c_out1=None, c_out2=None, topk: int = 0, topk_idx=None, timed: bool = False):
+    """The fused attention block; mutates ``o2``, the cache rows ``[past, past+S)`` and the c_out* tensors.
+    With ``timed`` the call waits for the stream and returns the four stage durations in ms."""
     lib = L.load()
     if x.dim() == 2:
         batch, (seq, hidden) = 1, x.shape
@@ -109,6 +110,10 @@ def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: in
         raise L.Tb200Error(-1, "tb200_attn_workspace_bytes")
     ws = Workspace.get(x.device, need, "attn")
     args.workspace, args.workspace_bytes = _ptr(ws), need
+    if timed:
+        ms = (C.c_float * 4)()
+        L.check(lib.tb200_attn_forward_timed(C.byref(args), _stream(), ms), "tb200_attn_forward_timed")
+        return list(ms)
     L.check(lib.tb200_attn_forward(C.byref(args), _stream()), "tb200_attn_forward")
 
 
