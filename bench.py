@@ -36,6 +36,7 @@ WORKLOADS = {
     "llama3_8b_qknorm_prefill_b8_s2048": dict(B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="qknorm"),
     "llama3_8b_prenorm_b8_s4096": dict(B=8, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="prenorm"),
     "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
+    "llama3_8b_vanilla_prefill_b2_s2048": dict(B=2, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),   # profiling size
     "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
 }
 DEFAULT = "llama3_8b_vanilla_prefill_b8_s2048"

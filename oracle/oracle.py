@@ -35,6 +35,7 @@ from __future__ import annotations
 import math
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 F32 = torch.float32
@@ -241,11 +242,24 @@ def ffn_block(
 # (``convert_eval_rms.py:127-176``, ``convert_ffn_llama.py:86-99``) and the benchmark configs'.
 # ----------------------------------------------------------------------------------------------
 
+class _Rng:
+    """Seeded N(0,1) / U(0,1) tensors from numpy's PCG64 stream: identical on every host CPU (torch's CPU
+    ``randn`` takes different vector paths on different machines, which would unpin the golden vectors)."""
+
+    def __init__(self, seed: int):
+        self.g = np.random.default_rng(seed)
+
+    def randn(self, *shape) -> torch.Tensor:
+        return torch.from_numpy(self.g.standard_normal(shape, dtype=np.float32))
+
+    def rand(self, *shape) -> torch.Tensor:
+        return torch.from_numpy(self.g.random(shape, dtype=np.float32))
+
+
 def ref_attention_inputs(M: int, N: int, D: int, P: int, seed: int = 42, std: float = 0.01):
     """Inputs of the reference parity driver (MHA, ``randn * 0.01``, unscaled ``randn`` noise)."""
-    g = torch.Generator().manual_seed(seed)
     H = N // D
-    rn = lambda *s: torch.randn(*s, generator=g, dtype=F32)
+    rn = _Rng(seed).randn
     return {
         "X": rn(M, N) * std, "WQ": rn(N, N) * std, "WK": rn(N, N) * std, "WV": rn(N, N) * std,
         "K_cache": rn(H, P + M, D) * std, "V_cache": rn(H, P + M, D) * std,
@@ -255,22 +269,26 @@ def ref_attention_inputs(M: int, N: int, D: int, P: int, seed: int = 42, std: fl
 
 def ref_ffn_inputs(M: int, N: int, P: int, seed: int = 42, std: float = 0.001):
     """Inputs of the reference FFN driver (``randn.clamp(-1,1) * 0.001``)."""
-    g = torch.Generator().manual_seed(seed)
-    rn = lambda *s: torch.randn(*s, generator=g, dtype=F32).clamp(-1, 1) * std
+    r = _Rng(seed)
+    rn = lambda *s: r.randn(*s).clamp(-1, 1) * std
     return {"O2": rn(M, N), "X": rn(M, N), "WO": rn(N, N), "WFF1a": rn(N, P), "WFF1b": rn(N, P), "WFF2": rn(P, N)}
 
 
-def gumbel_noise(shape, generator: torch.Generator) -> torch.Tensor:
-    """Gumbel(0,1) = -log(-log(U)), U clamped to [1e-9, 1-1e-9]."""
-    u = torch.rand(*shape, generator=generator, dtype=F32).clamp_(1e-9, 1 - 1e-9)
+def gumbel_noise(shape, generator) -> torch.Tensor:
+    """Gumbel(0,1) = -log(-log(U)), U clamped to [1e-9, 1-1e-9]; ``generator`` is a torch.Generator or an _Rng."""
+    if isinstance(generator, _Rng):
+        u = generator.rand(*shape)
+    else:
+        u = torch.rand(*shape, generator=generator, dtype=F32)
+    u = u.clamp_(1e-9, 1 - 1e-9)
     return -torch.log(-torch.log(u))
 
 
 def bench_attention_inputs(B: int, S: int, N: int, Hq: int, Hkv: int, D: int, seed: int = 0,
                            norm_weights: bool = False, noise: bool = False):
     """x ~ N(0,1); projection weights ~ N(0,0.02); norm weights 1 + N(0,0.02); Gumbel noise."""
-    g = torch.Generator().manual_seed(seed)
-    rn = lambda *s: torch.randn(*s, generator=g, dtype=F32)
+    g = _Rng(seed)
+    rn = g.randn
     t = {"X": rn(B, S, N), "WQ": rn(N, Hq * D) * 0.02, "WK": rn(N, Hkv * D) * 0.02, "WV": rn(N, Hkv * D) * 0.02}
     if norm_weights:
         t["norm_weight"] = 1 + rn(N) * 0.02
@@ -282,8 +300,7 @@ def bench_attention_inputs(B: int, S: int, N: int, Hq: int, Hkv: int, D: int, se
 
 
 def bench_ffn_inputs(M: int, N: int, P: int, seed: int = 0, gated: bool = True):
-    g = torch.Generator().manual_seed(seed)
-    rn = lambda *s: torch.randn(*s, generator=g, dtype=F32)
+    rn = _Rng(seed).randn
     t = {"X": rn(M, N), "W_gate": rn(N, P) * 0.02}
     if gated:
         t["W_up"] = rn(N, P) * 0.02

@@ -115,7 +115,12 @@ def main():
 
     # ---- small, self-contained ----
     for tag, (M, N, D, P) in {"a": (16, 128, 64, 48), "b": (8, 256, 128, 0), "c": (5, 192, 64, 33)}.items():
-        inp = orc.ref_attention_inputs(M, N, D, P, seed=42, std=0.2)
+        # well-conditioned scores for 16-bit kernels: x ~ N(0,1), weights ~ N(0,0.05), caches ~ N(0,0.5)
+        inp = orc.ref_attention_inputs(M, N, D, P, seed=42, std=1.0)
+        for name in ("WQ", "WK", "WV"):
+            inp[name] = inp[name] * 0.05
+        for name in ("K_cache", "V_cache"):
+            inp[name] = inp[name] * 0.5
         blob = {"shape": np.asarray([M, N, D, P])}
         blob.update({"in_" + k: v.numpy() for k, v in inp.items()})
         for cls in ATTN_CLASSES:

@@ -85,8 +85,7 @@ def test_gemm_is_deterministic(ops):
 def test_topk_is_a_stable_descending_sort(ops, rows, n, k):
     g = torch.Generator().manual_seed(n)
     s = torch.randn(rows, n, generator=g)
-    s[:, ::3] = s[:, 1::3][:, : s[:, ::3].shape[1]] if n >= 6 else s[:, ::3]     # plant ties
-    s = s.round(decimals=1)                                                          # many more ties
+    s = s.round(decimals=1)          # a grid of values: many exact ties
     got = ops.topk(s.to(dev()), k)
     assert torch.equal(got.cpu(), orc.stable_topk(s, k))
 
