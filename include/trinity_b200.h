@@ -29,7 +29,8 @@ typedef enum {
   TB200_ERR_UNSUPPORTED = -2,    /* a legal request this build has no kernel for */
   TB200_ERR_CUDA = -3,           /* a CUDA runtime/driver call failed */
   TB200_ERR_WORKSPACE = -4,      /* workspace missing or too small */
-  TB200_ERR_DEVICE_TIMEOUT = -5  /* a bounded device-side wait gave up (see tb200_device_status) */
+  TB200_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (see tb200_device_status) */
+  TB200_ERR_SCRATCH_LIMIT = -6   /* tb200_gemm_static_scratch: the partial sums exceed the built-in array */
 } tb200_status;
 
 typedef enum { TB200_F16 = 0, TB200_BF16 = 1, TB200_F32 = 2 } tb200_dtype;
@@ -72,6 +73,19 @@ typedef struct {
 } tb200_gemm_args;
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
 int tb200_gemm(const tb200_gemm_args* args, void* stream);
+/* No counterpart in the reference.  The same GEMM + epilogue as tb200_gemm, always computed as K slices
+ * whose fp32 partial sums go into a 16 MiB array that is part of the library image, so that the call
+ * performs NO device allocation at all (tb200_gemm's path creates a small per-device state with cudaMalloc
+ * on its first call and takes a caller-allocated workspace).  Meant for hosts that are not allowed to
+ * allocate: a server that gave all of HBM to its own pool, or code running under a foreign allocator.
+ *   - args->workspace / workspace_bytes are ignored; split_k 0 lets the library choose.
+ *   - split_k * m * n * 4 bytes (twice that with b2) must fit in 16 MiB, else TB200_ERR_SCRATCH_LIMIT.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls that may run concurrently on the GPU (different
+ *     streams) race on it.  Calls on one stream are ordered and safe.  Nothing in the array needs clearing
+ *     between calls: every partial sum that is read has been written by the same call. */
+int tb200_gemm_static_scratch(const tb200_gemm_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Fused attention block -- replaces kernel_0/kernel_1 of the emitted attention modules:

@@ -60,6 +60,7 @@ SYMBOLS = {
     "tb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_int, C.c_void_p]),
     "tb200_gemm_workspace_bytes": (C.c_size_t, [C.POINTER(GemmArgs)]),
     "tb200_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "tb200_gemm_static_scratch": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "tb200_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "tb200_attn_forward": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "tb200_attn_forward_timed": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.POINTER(C.c_float)]),

@@ -548,4 +548,139 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
+// ====================================================================================================
+// Split-K GEMM whose scratch lives in the library image (no device allocation anywhere on the path).
+//
+// Some hosts of this library may not allocate device memory: an inference server that hands every byte
+// of HBM to its own pool at start-up, or a plugin running inside someone else's allocator, cannot let a
+// callee reach for cudaMalloc.  For them the fp32 partial sums of the K slices go into the fixed array
+// below instead of a caller- or library-allocated workspace.  Every GPU that loads the library carries
+// the array (kStaticScratchBytes) until the process exits.
+//
+// `g_static_scratch` and `g_static_err` are DEVICE symbols.  In host code their names are only handles:
+// the device addresses are fetched once per device with cudaGetSymbolAddress (that device current) and
+// it is those addresses that are passed to the kernels.
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ int g_static_err;  // zero-initialised; the kernels' bounded waits report here
+
+namespace {
+
+struct StaticState {
+  bool ready = false;
+  int num_sms = 0;
+  float* scratch = nullptr;
+  int* err = nullptr;
+};
+StaticState g_static_state[32];
+
+// First call on a device: resolve the symbols' device addresses.  Allocates nothing.
+int static_state(StaticState** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 32) return TB200_ERR_CUDA;
+  StaticState& st = g_static_state[dev];
+  if (!st.ready) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return TB200_ERR_CUDA;
+    if (major != 10) return TB200_ERR_UNSUPPORTED;
+    if (cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TB200_ERR_CUDA;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return TB200_ERR_CUDA;
+    st.scratch = static_cast<float*>(p);
+    p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_err) != cudaSuccess || p == nullptr) return TB200_ERR_CUDA;
+    st.err = static_cast<int*>(p);
+    int status = ensure_tensor_map_encoder();
+    if (status != TB200_OK) return status;
+    st.ready = true;
+  }
+  *out = &st;
+  return TB200_OK;
+}
+
+}  // namespace
+
+int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
+  if (a == nullptr) return TB200_ERR_INVALID;
+  if (a->dtype != TB200_BF16 && a->dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
+  if (a->m < 0 || a->n <= 0 || a->k <= 0 || (a->n & 7) || (a->k & 7)) return TB200_ERR_INVALID;
+  if (a->m > (1 << 30) || a->n > (1 << 30) || a->k > (1 << 30)) return TB200_ERR_INVALID;
+  if (!a->a || !a->b || !a->c || (a->act != 0 && a->act != 1) || a->split_k < 0) return TB200_ERR_INVALID;
+  if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->b2) || !aligned16(a->c) || !aligned16(a->residual)) return TB200_ERR_INVALID;
+  if (a->m == 0) return TB200_OK;
+  StaticState* st = nullptr;
+  int status = static_state(&st);
+  if (status != TB200_OK) return status;
+
+  const int M = static_cast<int>(a->m), N = static_cast<int>(a->n), K = static_cast<int>(a->k);
+  const bool gated = a->b2 != nullptr;
+  const int n_src = gated ? 2 : 1;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.K = K;
+  p.k_blocks = (K + BK - 1) / BK;
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = n_src * ((N + BN - 1) / BN);
+  int split = a->split_k;
+  if (split == 0) {  // as many slices as fill the SMs once, at least four K blocks each
+    split = st->num_sms / (p.m_tiles * p.n_tiles);
+    if (split > p.k_blocks / 4) split = p.k_blocks / 4;
+    if (split > 32) split = 32;
+    if (split < 1) split = 1;
+  }
+  if (split > p.k_blocks) split = p.k_blocks;
+  p.kb_per_split = (p.k_blocks + split - 1) / split;
+  p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  const size_t need = static_cast<size_t>(p.split_k) * M * n_src * N * sizeof(float);
+  if (need > kStaticScratchBytes) return TB200_ERR_SCRATCH_LIMIT;
+  p.n_src = n_src;
+  p.tile_n = BN;
+  for (int s = 0; s < n_src; ++s) {
+    p.src_n[s] = N;
+    p.src_tile0[s] = s * ((N + BN - 1) / BN);
+  }
+  for (int s = n_src; s < 4; ++s) p.src_tile0[s] = p.n_tiles;
+  p.total_units = p.m_tiles * p.n_tiles * p.split_k;
+  p.err = st->err;
+  p.partial = st->scratch;
+  p.ldp = static_cast<long long>(n_src) * N;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    const uint32_t box[2] = {BK, BM};
+    if ((status = make_tensor_map(&p.map_a, a->a, 2, dims, strides, box)) != TB200_OK) return status;
+  }
+  const void* srcs[2] = {a->b, a->b2};
+  for (int s = 0; s < n_src; ++s) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, BK};
+    if ((status = make_tensor_map(&p.map_b[s], srcs[s], 2, dims, strides, box)) != TB200_OK) return status;
+  }
+  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
+  status = (a->dtype == TB200_BF16) ? launch_typed<__nv_bfloat16>(p, GEMM_PARTIAL, grid, stream)
+                                    : launch_typed<__half>(p, GEMM_PARTIAL, grid, stream);
+  if (status != TB200_OK) return status;
+  SplitKFinish f;
+  f.dtype = a->dtype;
+  f.M = M;
+  f.N = N;
+  f.split_k = p.split_k;
+  f.partial = st->scratch;
+  f.ldp = p.ldp;
+  f.gated = gated ? 1 : 0;
+  f.act = a->act;
+  f.row_scale = a->row_scale;
+  f.residual = a->residual;
+  f.ldr = N;
+  f.C = a->c;
+  f.ldc = N;
+  return launch_splitk_finish(f, stream);
+}
+
 }  // namespace tb200
+
+extern "C" int tb200_gemm_static_scratch(const tb200_gemm_args* args, void* stream) {
+  return tb200::gemm_splitk_static(args, static_cast<cudaStream_t>(stream));
+}

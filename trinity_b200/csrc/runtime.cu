@@ -55,6 +55,19 @@ DeviceState* device_state(int* status) {
   return &st;
 }
 
+// Resolve cuTensorMapEncodeTiled without creating the per-device state (no device allocation).
+int ensure_tensor_map_encoder() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (g_encode) return TB200_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+      qres != cudaDriverEntryPointSuccess)
+    return TB200_ERR_CUDA;
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return TB200_OK;
+}
+
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                     const uint32_t* box) {
   if (!g_encode) return TB200_ERR_CUDA;
@@ -86,6 +99,7 @@ const char* tb200_strerror(int status) {
     case TB200_ERR_CUDA: return "a CUDA call failed";
     case TB200_ERR_WORKSPACE: return "workspace missing or too small";
     case TB200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case TB200_ERR_SCRATCH_LIMIT: return "the problem needs more scratch than the library's built-in 16 MiB array";
     default: return "unknown status";
   }
 }
