@@ -1,0 +1,140 @@
+"""Multi-rank host logic on CPU: world_size-2 gloo processes drive trinity_b200.shard with an fp32 stand-in for the
+local GPU operators and must reproduce the unsharded oracle."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle as orc
+from trinity_b200 import shard
+
+
+class Fp32Ops:
+    """fp32 torch stand-in for the local operators (the GPU path calls the C ABI instead)."""
+
+    def gemm(self, a, b, *, b2=None, row_scale=None, residual=None, act=0):
+        r = a @ b
+        if row_scale is not None:
+            r = r * row_scale[:, None]
+        if b2 is not None:
+            u = a @ b2
+            if row_scale is not None:
+                u = u * row_scale[:, None]
+            r = torch.nn.functional.silu(r) * u
+        if act == 1:
+            r = torch.nn.functional.gelu(r)
+        if residual is not None:
+            r = r + residual
+        return r
+
+    def row_inv_rms(self, a, eps):
+        return torch.rsqrt(a.pow(2).mean(-1) + eps)
+
+    def rmsnorm(self, a, weight, eps):
+        return orc.rmsnorm(a, weight, eps)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ffn_worker(rank, world, port, case, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        t = orc.ref_ffn_inputs(12, 64, 96, seed=5, std=0.3)
+        gelu = case == "gelu"
+        sh = shard.shard_ffn_weights(t["WFF1b"], None if gelu else t["WFF1a"], t["WFF2"], None if case == "plain" or gelu else t["WO"],
+                                     rank, world)
+        o2_local = None
+        if sh.wo is not None:
+            n = t["O2"].shape[1] // world
+            o2_local = t["O2"][:, rank * n:(rank + 1) * n].contiguous()
+        out = shard.tensor_parallel_ffn(t["X"], sh, act="gelu" if gelu else "swiglu", o2_local=o2_local,
+                                        norm=case in ("block", "tail"), falcon_tail=case == "tail", local_ops=Fp32Ops())
+        if rank == 0:
+            ret.put({k: v.clone() for k, v in out.items()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["plain", "gelu", "block", "tail"])
+def test_tensor_parallel_ffn_two_ranks(case):
+    ctx = mp.get_context("spawn")
+    ret = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ffn_worker, args=(r, 2, port, case, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = ret.get()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    t = orc.ref_ffn_inputs(12, 64, 96, seed=5, std=0.3)
+    if case == "plain":
+        want = orc.ffn_block(t["X"], t["WFF1b"], t["WFF1a"], t["WFF2"])
+        torch.testing.assert_close(got["FF2"], want["FF2"], rtol=1e-5, atol=1e-6)
+    elif case == "gelu":
+        want = orc.ffn_block(t["X"], t["WFF1b"], None, t["WFF2"], act="gelu")
+        torch.testing.assert_close(got["FF2"], want["FF2"], rtol=1e-5, atol=1e-6)
+    else:
+        want = orc.ffn_block(t["O2"], t["WFF1b"], t["WFF1a"], t["WFF2"], wo=t["WO"], residual=t["X"], norm=True,
+                             falcon_tail=case == "tail")
+        torch.testing.assert_close(got["attn_O2"], want["attn_O2"], rtol=1e-5, atol=1e-6)
+        key = "O_FF_norm" if case == "tail" else "FF2"
+        torch.testing.assert_close(got[key], want[key], rtol=1e-4, atol=1e-6)
+
+
+def _attn_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, S, N, Hq, Hkv, D, P = 2, 10, 64, 4, 2, 16, 6
+        t = orc.bench_attention_inputs(B, S, N, Hq, Hkv, D, seed=2)
+        r = orc._Rng(7)
+        kc, vc = r.randn(B, Hkv, P + S, D), r.randn(B, Hkv, P + S, D)
+        wq, wk, wv = shard.shard_attention_weights(t["WQ"], t["WK"], t["WV"], D, rank, world)
+        out = orc.attention_block(t["X"], wq, wk, wv, shard.shard_heads(kc, Hkv, rank, world, 1), shard.shard_heads(vc, Hkv, rank, world, 1),
+                                  past=P, head_dim=D, causal=True, sm_scale=D ** -0.5, roco=True)
+        full = shard.gather_columns(out["O2"])
+        if rank == 0:
+            ret.put((full.clone(), out["C_out1"].clone()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_group_sharded_attention_two_ranks():
+    ctx = mp.get_context("spawn")
+    ret = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_attn_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    full, c1_rank0 = ret.get()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    B, S, N, Hq, Hkv, D, P = 2, 10, 64, 4, 2, 16, 6
+    t = orc.bench_attention_inputs(B, S, N, Hq, Hkv, D, seed=2)
+    r = orc._Rng(7)
+    kc, vc = r.randn(B, Hkv, P + S, D), r.randn(B, Hkv, P + S, D)
+    want = orc.attention_block(t["X"], t["WQ"], t["WK"], t["WV"], kc, vc, past=P, head_dim=D, causal=True, sm_scale=D ** -0.5, roco=True)
+    torch.testing.assert_close(full, want["O2"], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(c1_rank0, want["C_out1"][:, :2], rtol=1e-5, atol=1e-6)   # rank 0 owns q heads 0..1
+
+
+def test_slices_and_errors():
+    qs, kvs = shard.head_group_slices(32, 8, 128, rank=3, world=4)
+    assert (qs.start, qs.stop, kvs.start, kvs.stop) == (3 * 8 * 128, 4 * 8 * 128, 3 * 2 * 128, 4 * 2 * 128)
+    with pytest.raises(ValueError, match="shard by batch"):
+        shard.head_group_slices(71, 1, 64, rank=0, world=2)          # Falcon MQA cannot split its single KV head
+    parts = [shard.batch_slice(16, r, 3) for r in range(3)]
+    assert [p.stop - p.start for p in parts] == [6, 5, 5] and parts[0].start == 0 and parts[-1].stop == 16
+    with pytest.raises(ValueError):
+        shard.shard_ffn_weights(torch.zeros(8, 20), torch.zeros(8, 20), torch.zeros(20, 8), None, 0, 2)

@@ -67,6 +67,17 @@ def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float =
     return out
 
 
+def row_inv_rms(x: torch.Tensor, eps: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Only the per-row statistic ``rsqrt(mean(x^2) + eps)`` (fp32), for the norm-as-epilogue path."""
+    lib = L.load()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=x.device)
+    L.check(lib.tb200_rmsnorm(_ptr(x), None, None, _ptr(out), rows, cols, eps, _dt(x), _stream()), "tb200_rmsnorm")
+    return out
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, b2: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: int = 0, split_k: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = L.load()
