@@ -38,6 +38,10 @@ WORKLOADS = {
     "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
     "llama3_8b_vanilla_prefill_b2_s2048": dict(B=2, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),   # profiling size
     "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
+    # FFN blocks: M tokens, N hidden, P inner
+    "llama3_8b_swiglu_ffn_m64": dict(kind="ffn", M=64, N=4096, P=14336, act="swiglu", dtype="fp16"),
+    "llama3_8b_swiglu_ffn_m16384": dict(kind="ffn", M=16384, N=4096, P=14336, act="swiglu", dtype="bf16"),
+    "falcon_7b_gelu_ffn_m32768": dict(kind="ffn", M=32768, N=4544, P=18176, act="gelu", dtype="bf16"),
 }
 DEFAULT = "llama3_8b_vanilla_prefill_b8_s2048"
 
@@ -161,6 +165,142 @@ def run_reference(args, w, name):
     print(json.dumps(line), flush=True)
 
 
+def run_ffn(args, w, name):
+    """FFN block: act(x @ W_gate [, x @ W_up]) @ W_down.  One GPU: tb200_ffn_forward.  N GPUs: tensor-parallel
+    (column-parallel up, row-parallel down, one NCCL all-reduce), total work fixed -> strong scaling."""
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    from trinity_b200 import _lib as L
+    from trinity_b200 import ops, shard
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
+    M, N, P = w["M"], w["N"], w["P"]
+    gated = w["act"] == "swiglu"
+    host = {k: v.to(dtype) for k, v in orc.bench_ffn_inputs(M, N, P, seed=0, gated=gated).items()}
+    x = host["X"].to(dev)
+    weight_bytes = (3 if gated else 2) * N * P * 2
+    copies = 2 if weight_bytes < 1.5e9 else 1        # rotate weight copies so that no step finds its weights in L2
+    sets = []
+    for _ in range(copies):
+        sh = shard.shard_ffn_weights(host["W_gate"], host.get("W_up"), host["W_down"], None, rank, world)
+        sets.append(shard.FfnShard(sh.w_gate.to(dev), None if sh.w_up is None else sh.w_up.to(dev), sh.w_down.to(dev), None))
+    ff2 = torch.zeros(M, N, dtype=dtype, device=dev)
+    act = L.FFN_SWIGLU if gated else L.FFN_GELU
+    it = [0]
+
+    def step():
+        s_ = sets[it[0] % copies]
+        it[0] += 1
+        if world == 1:
+            ops.ffn_forward(x, s_.w_gate, s_.w_up, s_.w_down, ff2, act=act)
+            return ff2
+        return shard.tensor_parallel_ffn(x, s_, act=w["act"])["FF2"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ops.device_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    # stage split with the building-block GEMMs (same kernels the block chains)
+    ff1 = torch.empty(M, P // world, dtype=dtype, device=dev)
+    st_ms = [0.0, 0.0]
+    for i in range(args.steps):
+        s_ = sets[i % copies]
+        a0, a1, a2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a0.record()
+        ops.gemm(x, s_.w_gate, b2=s_.w_up, act=0 if gated else 1, split_k=0, out=ff1)
+        a1.record()
+        ops.gemm(ff1, s_.w_down, split_k=0, out=ff2)
+        a2.record()
+        torch.cuda.synchronize()
+        st_ms[0] += a0.elapsed_time(a1) / args.steps
+        st_ms[1] += a1.elapsed_time(a2) / args.steps
+    # end to end: pinned host x in, ff2 out
+    x_host = host["X"].pin_memory()
+    o_host = torch.empty(M, N, dtype=dtype).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        o_host.copy_(step(), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    ops.device_status()
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    flops = 2.0 * M * N * P * (3 if gated else 2)
+    algo_bytes = weight_bytes + 2 * M * N * 2
+    peaks = load_peaks()
+    if rank == 0:
+        ai = flops / algo_bytes
+        hbm_bound = ai < peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+        up_bytes = (2 if gated else 1) * N * P * 2 / world + M * N * 2 + M * P * 2 / world
+        up_flops = 2.0 * M * N * P * (2 if gated else 1) / world
+        if hbm_bound:
+            roof = {"bound": "hbm", "kernel": "gemm_kernel (gate/up projection, K-sliced) + splitk_finish", "achieved": up_bytes / (st_ms[0] * 1e-3) / 1e9,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "bytes_per_launch": up_bytes}
+        else:
+            roof = {"bound": "tensor", "kernel": "gemm_kernel (gate/up projection)", "achieved": up_flops / (st_ms[0] * 1e-3) / 1e12,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "flops_per_launch": up_flops}
+        roof.update(frac=roof["achieved"] / roof["peak"], peak_source=peaks["source"], traffic=None, ms_per_launch=st_ms[0])
+        line = {
+            "metric": "fused_block_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_call": ms * 1e3, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": name, "tokens": M, "hidden": N, "inner": P, "act": w["act"],
+                       "parallelism": "single GPU" if world == 1 else f"tensor-parallel x{world}, one NCCL all-reduce",
+                       "l2": f"{copies} rotating weight sets of {weight_bytes / 1e6:.0f} MB each (> 126 MB L2)"},
+            "block_hbm_gbs": algo_bytes / world / (ms * 1e-3) / 1e9, "block_frac_of_hbm": algo_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "block_frac_of_tensor_peak": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": M * N * 2,
+                    "d2h_bytes_per_step": M * N * 2, "api": "ops.ffn_forward / shard.tensor_parallel_ffn"},
+            "gpu_launches": None, "roofline": roof,
+            "stages": {"up_ms": st_ms[0], "down_ms": st_ms[1]}, "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count())
+            rows = min(M, 256)
+            t0 = time.perf_counter()
+            orc.ffn_block(host["X"][:rows].float(), host["W_gate"].float(), host["W_up"].float() if gated else None, host["W_down"].float(), act=w["act"])
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": flops * rows / M / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "seconds": dt,
+                                    "sample": f"{rows} of {M} tokens, 1 pass, fp32 oracle port of baseline/ffn_ref.py"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,6 +311,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
+    if w.get("kind") == "ffn":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the attention workloads")
+        return run_ffn(args, w, args.workload)
     if args.impl == "reference":
         return run_reference(args, w, args.workload)
     if args.warmup < 3:

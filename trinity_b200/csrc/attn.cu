@@ -14,6 +14,7 @@
 //
 // KeyFormer (NOISE): the same pass also keeps the online log-sum-exp of (scale*s + noise)/tau per row.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -394,6 +395,11 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   if (!a.q || !a.k_cache || !a.v_cache || !a.o2) return TB200_ERR_INVALID;
   if (!aligned16(a.q) || !aligned16(a.k_cache) || !aligned16(a.v_cache) || !aligned16(a.o2) || !aligned16(a.noise)) return TB200_ERR_INVALID;
   if (a.Hq > 65535 || a.B > 65535) return TB200_ERR_INVALID;
+  if (!(a.sm_scale > 0.f)) return TB200_ERR_INVALID;  // the row maximum is taken before scaling
+  if (a.noise == nullptr) {
+    static const bool single_tile = getenv("TB200_ATTN_SINGLE_TILE") != nullptr;  // A/B switch for measurements
+    if (!single_tile) return launch_attn_fwd_pingpong(a, stream);
+  }
 
   AttnParams p;
   memset(&p, 0, sizeof(p));

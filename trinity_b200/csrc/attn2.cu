@@ -1,0 +1,360 @@
+// Attention forward, two query tiles per CTA ("ping-pong"): the kernel used when no noise tensor is involved.
+//
+// One CTA per (256 queries, q head, batch element), 320 threads:
+//   warp 0      TMA producer: both Q tiles once, then K and V tiles of 128 keys through two-deep rings
+//   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}
+//   warps 2-5   softmax of query tile 0          warps 6-9   softmax of query tile 1
+// While one softmax warpgroup works on its S tile the tensor core serves the other tile, and each SM sub-partition
+// holds two softmax warps whose MUFU / FMA / TMEM latencies overlap.  K and V tiles are fetched once for 256 queries.
+//
+// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
+// P_j (16-bit) is written back over the first 64 columns of its own S tile and is the A operand of P_j V_j straight
+// from tensor memory (no shared-memory round trip).  MMAs issued by one thread complete in issue order, so S_{j+1}
+// (issued after P_j V_j) cannot overwrite P_j early, and an arrival on s_full also means the previous P V is done.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tb200 {
+
+namespace {
+
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;
+
+template <int D> struct Smem2 {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kQOff = 0;                 // two query tiles
+  static constexpr int kKOff = 2 * kTile;         // two stages
+  static constexpr int kVOff = 4 * kTile;         // two stages
+  static constexpr int kBarOff = 6 * kTile;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+struct Attn2Params {
+  CUtensorMap map_q, map_k, map_v;
+  int B, S, Hq, Hkv, past, kv_len, causal;
+  float scale_log2;
+  void* o2;
+  float* lse2;
+  int* err;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_constant__ Attn2Params p) {
+  using L = Smem2<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2] per query tile
+  uint64_t* p_ready = bars + 11;  // [2] per query tile
+  uint64_t* pv_done = bars + 13;  // [2] per query tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_blocks = (p.S + 2 * BQ - 1) / (2 * BQ);
+  const int q0 = (n_blocks - 1 - blockIdx.x) * 2 * BQ;  // longest blocks first
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = hq / (p.Hq / p.Hkv);
+  int nt[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0t = q0 + t * BQ;
+    int last_key = p.kv_len - 1;
+    if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
+    nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
+  }
+  const int nt_max = max(nt[0], nt[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&pv_done[i], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&p.map_q);
+    tma_prefetch_desc(&p.map_k);
+    tma_prefetch_desc(&p.map_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const AbortCtx ctx{p.err, abort_flag};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 2 * L::kTile);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int dc = 0; dc < D / 64; ++dc)
+          tma_load_3d(smem + L::kQOff + t * L::kTile + dc * (BQ * 128), &p.map_q, q_full, dc * 64, q0 + t * BQ, b * p.Hq + hq);
+    }
+    __syncwarp();
+    for (int j = 0; j < nt_max; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&k_empty[st], ph ^ 1, ctx, 401)) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&k_full[st], L::kTile);
+#pragma unroll
+        for (int dc = 0; dc < D / 64; ++dc)
+          tma_load_3d(smem + L::kKOff + st * L::kTile + dc * (BKV * 128), &p.map_k, &k_full[st], dc * 64, j * BKV, b * p.Hkv + hkv);
+      }
+      __syncwarp();
+      if (!mbar_wait(&v_empty[st], ph ^ 1, ctx, 402)) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&v_full[st], L::kTile);
+#pragma unroll
+        for (int dc = 0; dc < D / 64; ++dc)
+          tma_load_3d(smem + L::kVOff + st * L::kTile + dc * (BKV * 128), &p.map_v, &v_full[st], dc * 64, j * BKV, b * p.Hkv + hkv);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_s = make_idesc(IsBf16<T>::value, false, false, BQ, BKV);
+    constexpr uint32_t idesc_o = make_idesc(IsBf16<T>::value, false, true, BQ, D);
+    auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
+      const uint32_t q_s = smem_u32(smem + L::kQOff + t * L::kTile);
+      const uint32_t k_s = smem_u32(smem + L::kKOff + (j & 1) * L::kTile);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+        umma_ss(tmem_base + t * BKV, make_smem_desc(q_s + off, 16, 1024), make_smem_desc(k_s + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(&s_full[t]);
+    };
+    auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j, P_t read from tensor memory
+      const uint32_t v_s = smem_u32(smem + L::kVOff + (j & 1) * L::kTile);
+#pragma unroll
+      for (int kk = 0; kk < BKV / 16; ++kk)
+        umma_ts(tmem_base + 2 * BKV + t * D, tmem_base + t * BKV + kk * 8, make_smem_desc(v_s + kk * 2048, BKV * 128, 1024), idesc_o,
+                (j > 0 || kk > 0) ? 1u : 0u);
+      umma_commit(&pv_done[t]);
+    };
+    bool ok = mbar_wait(q_full, 0, ctx, 403) && mbar_wait(&k_full[0], 0, ctx, 404);
+    if (ok) {
+      tc_fence_after();
+      if (lane == 0) {
+        if (nt[0] > 0) issue_s(0, 0);
+        if (nt[1] > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      __syncwarp();
+    }
+    for (int j = 0; ok && j < nt_max; ++j) {
+      if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, ctx, 405)) break;
+      bool k_ready = false;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (j < nt[t]) {
+          if (!mbar_wait(&p_ready[t], j & 1, ctx, 406)) { ok = false; break; }
+          tc_fence_after();
+          if (lane == 0) issue_pv(t, j);
+          __syncwarp();
+        }
+        if (t == 1) {
+          if (lane == 0) umma_commit(&v_empty[j & 1]);
+          __syncwarp();
+        }
+        if (j + 1 < nt[t]) {
+          if (!k_ready) {
+            if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, 407)) { ok = false; break; }
+            tc_fence_after();
+            k_ready = true;
+          }
+          if (lane == 0) issue_s(t, j + 1);
+          __syncwarp();
+        }
+      }
+      if (ok && j + 1 < nt_max) {
+        if (lane == 0) umma_commit(&k_empty[(j + 1) & 1]);
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warpgroups
+    const int t = (warp - 2) >> 2;  // query tile of this warpgroup
+    const int quad = warp & 3;
+    const int r_in = quad * 32 + lane;
+    const int qi = q0 + t * BQ + r_in;
+    const bool row_ok = qi < p.S;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + t * BKV + lane_sel;
+    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
+    const int key_limit = p.causal ? min(p.past + qi, p.kv_len - 1) : p.kv_len - 1;
+    const int my_nt = nt[t];
+    float m_use = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < my_nt; ++j) {
+      const int k0 = j * BKV;
+      if (!mbar_wait(&s_full[t], j & 1, ctx, 408)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s[BKV];
+      tmem_ld_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_x32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_x32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_wait_ld();
+
+      float rowmax = -INFINITY;
+      if (k0 + BKV - 1 > key_limit) {  // tile touches the causal diagonal or the end of the keys
+#pragma unroll
+        for (int i = 0; i < BKV; ++i) {
+          if (k0 + i > key_limit) s[i] = 0xff800000u;  // -inf
+          rowmax = fmaxf(rowmax, __uint_as_float(s[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BKV; ++i) rowmax = fmaxf(rowmax, __uint_as_float(s[i]));
+      }
+      const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
+      const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
+      float alpha = 1.f;
+      if (grow) {
+        alpha = fast_exp2(m_use - m_new);
+        m_use = m_new;
+      }
+      const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
+      float rowsum = 0.f;
+      uint32_t pk[BKV / 2];
+#pragma unroll
+      for (int i = 0; i < BKV; i += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_mref));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_mref));
+        rowsum += p0 + p1;
+        pk[i >> 1] = Pack2<T>::pack(p0, p1);
+      }
+      l = l * alpha + rowsum;
+
+      // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        uint32_t o[32];
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld_x32(tmem_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(tmem_o + c * 32, o);
+        }
+      }
+      tmem_st_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_ready[t]);
+    }
+
+    if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
+      tc_fence_after();
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(b) * p.S + qi) * p.Hq + hq) * D;
+      uint32_t o[32];
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        tmem_ld_x32(tmem_o + c * 32, o);
+        tmem_wait_ld();
+        if (row_ok) {
+          uint4* d = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            d[i] = make_uint4(Pack2<T>::pack(__uint_as_float(o[8 * i]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l),
+                              Pack2<T>::pack(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l),
+                              Pack2<T>::pack(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l),
+                              Pack2<T>::pack(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l));
+        }
+      }
+      if (row_ok && p.lse2 != nullptr) p.lse2[(static_cast<long long>(b) * p.Hq + hq) * p.S + qi] = m_use + log2f(l);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T, int D>
+int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
+  static bool attr_set[32] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 31]) {
+    if (cudaFuncSetAttribute(attn_fwd2_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<D>::kTotal) != cudaSuccess)
+      return TB200_ERR_CUDA;
+    attr_set[dev & 31] = true;
+  }
+  attn_fwd2_kernel<T, D><<<grid, kThreads, Smem2<D>::kTotal, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
+
+}  // namespace
+
+// Same contract as launch_attn_fwd without the KeyFormer statistic; arguments are validated by the caller.
+int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  Attn2Params p;
+  memset(&p, 0, sizeof(p));
+  p.B = a.B; p.S = a.S; p.Hq = a.Hq; p.Hkv = a.Hkv; p.past = a.past; p.kv_len = a.past + a.S; p.causal = a.causal;
+  p.scale_log2 = a.sm_scale * kLog2e;
+  p.o2 = a.o2;
+  p.lse2 = a.lse2;
+  p.err = st->err_word;
+  const uint64_t D = static_cast<uint64_t>(a.D);
+  {
+    const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
+    const uint64_t strides[2] = {D * 2, static_cast<uint64_t>(a.S) * D * 2};
+    const uint32_t box[3] = {64, BQ, 1};
+    if ((status = make_tensor_map(&p.map_q, a.q, 3, dims, strides, box)) != TB200_OK) return status;
+  }
+  {
+    const uint64_t dims[3] = {D, static_cast<uint64_t>(p.kv_len), static_cast<uint64_t>(a.B) * a.Hkv};
+    const uint64_t strides[2] = {D * 2, static_cast<uint64_t>(a.cache_len) * D * 2};
+    const uint32_t box[3] = {64, BKV, 1};
+    if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
+    if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
+  }
+  const dim3 grid((a.S + 2 * BQ - 1) / (2 * BQ), a.Hq, a.B);
+  if (a.dtype == TB200_BF16) {
+    return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
+  }
+  return a.D == 128 ? launch_one<__half, 128>(p, grid, stream) : launch_one<__half, 64>(p, grid, stream);
+}
+
+}  // namespace tb200

@@ -110,6 +110,8 @@ struct AttnLaunch {
   float* lse2_perturbed = nullptr;  // (B,Hq,S)
 };
 int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream);
+// attn2.cu: two query tiles per CTA; chosen by launch_attn_fwd when there is no noise tensor
+int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream);
 
 // ---------------------------------------------------------------- score.cu
 struct ScoreLaunch {
