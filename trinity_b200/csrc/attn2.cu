@@ -12,6 +12,7 @@
 // from tensor memory (no shared-memory round trip).  MMAs issued by one thread complete in issue order, so S_{j+1}
 // (issued after P_j V_j) cannot overwrite P_j early, and an arrival on s_full also means the previous P V is done.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -44,7 +45,14 @@ struct Attn2Params {
   void* o2;
   float* lse2;
   int* err;
+  long long* trace;  // timing probes (TB200_TRACE builds only)
 };
+
+#ifdef TB200_TRACE
+#define TRACE(slot, cond) do { if ((cond) && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[(slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot, cond) do { } while (0)
+#endif
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_constant__ Attn2Params p) {
@@ -144,33 +152,34 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc(IsBf16<T>::value, false, false, BQ, BKV);
     constexpr uint32_t idesc_o = make_idesc(IsBf16<T>::value, false, true, BQ, D);
+    // All 32 lanes run this code converged with warp-uniform operands; one elected lane issues (see common.cuh).
+    const uint32_t q_base = smem_u32(smem + L::kQOff);
+    const uint32_t k_base = smem_u32(smem + L::kKOff);
+    const uint32_t v_base = smem_u32(smem + L::kVOff);
     auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
-      const uint32_t q_s = smem_u32(smem + L::kQOff + t * L::kTile);
-      const uint32_t k_s = smem_u32(smem + L::kKOff + (j & 1) * L::kTile);
+      const uint64_t qd = make_smem_desc(q_base + t * L::kTile, 16, 1024);
+      const uint64_t kd = make_smem_desc(k_base + (j & 1) * L::kTile, 16, 1024);
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-        umma_ss(tmem_base + t * BKV, make_smem_desc(q_s + off, 16, 1024), make_smem_desc(k_s + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);  // start-address field
+        umma_ss_warp(tmem_base + t * BKV, qd + off, kd + off, idesc_s, kk > 0 ? 1u : 0u);
       }
-      umma_commit(&s_full[t]);
+      umma_commit_warp(&s_full[t]);
     };
     auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j, P_t read from tensor memory
-      const uint32_t v_s = smem_u32(smem + L::kVOff + (j & 1) * L::kTile);
+      const uint64_t vd = make_smem_desc(v_base + (j & 1) * L::kTile, BKV * 128, 1024);
 #pragma unroll
       for (int kk = 0; kk < BKV / 16; ++kk)
-        umma_ts(tmem_base + 2 * BKV + t * D, tmem_base + t * BKV + kk * 8, make_smem_desc(v_s + kk * 2048, BKV * 128, 1024), idesc_o,
-                (j > 0 || kk > 0) ? 1u : 0u);
-      umma_commit(&pv_done[t]);
+        umma_ts_warp(tmem_base + 2 * BKV + t * D, tmem_base + t * BKV + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
+                     (j > 0 || kk > 0) ? 1u : 0u);
+      umma_commit_warp(&pv_done[t]);
     };
     bool ok = mbar_wait(q_full, 0, ctx, 403) && mbar_wait(&k_full[0], 0, ctx, 404);
     if (ok) {
       tc_fence_after();
-      if (lane == 0) {
-        if (nt[0] > 0) issue_s(0, 0);
-        if (nt[1] > 0) issue_s(1, 0);
-        umma_commit(&k_empty[0]);
-      }
-      __syncwarp();
+      if (nt[0] > 0) issue_s(0, 0);
+      if (nt[1] > 0) issue_s(1, 0);
+      umma_commit_warp(&k_empty[0]);
     }
     for (int j = 0; ok && j < nt_max; ++j) {
       if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, ctx, 405)) break;
@@ -180,27 +189,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         if (j < nt[t]) {
           if (!mbar_wait(&p_ready[t], j & 1, ctx, 406)) { ok = false; break; }
           tc_fence_after();
-          if (lane == 0) issue_pv(t, j);
-          __syncwarp();
+          TRACE(512 + (t * 32 + j) * 4 + 0, lane == 0 && j < 32);
+          issue_pv(t, j);
+          TRACE(512 + (t * 32 + j) * 4 + 1, lane == 0 && j < 32);
         }
-        if (t == 1) {
-          if (lane == 0) umma_commit(&v_empty[j & 1]);
-          __syncwarp();
-        }
+        if (t == 1) umma_commit_warp(&v_empty[j & 1]);
         if (j + 1 < nt[t]) {
           if (!k_ready) {
             if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, 407)) { ok = false; break; }
             tc_fence_after();
             k_ready = true;
           }
-          if (lane == 0) issue_s(t, j + 1);
-          __syncwarp();
+          issue_s(t, j + 1);
+          TRACE(512 + (t * 32 + j) * 4 + 2, lane == 0 && j < 32);
         }
       }
-      if (ok && j + 1 < nt_max) {
-        if (lane == 0) umma_commit(&k_empty[(j + 1) & 1]);
-        __syncwarp();
-      }
+      if (ok && j + 1 < nt_max) umma_commit_warp(&k_empty[(j + 1) & 1]);
     }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
@@ -219,26 +223,33 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
 
     for (int j = 0; j < my_nt; ++j) {
       const int k0 = j * BKV;
+      TRACE((t * 32 + j) * 8 + 0, r_in == 0 && j < 32);
       if (!mbar_wait(&s_full[t], j & 1, ctx, 408)) { ok = false; break; }
       tc_fence_after();
+      TRACE((t * 32 + j) * 8 + 1, r_in == 0 && j < 32);
       uint32_t s[BKV];
       tmem_ld_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_ld_x32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld_x32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_wait_ld();
+      TRACE((t * 32 + j) * 8 + 2, r_in == 0 && j < 32);
 
-      float rowmax = -INFINITY;
       if (k0 + BKV - 1 > key_limit) {  // tile touches the causal diagonal or the end of the keys
 #pragma unroll
-        for (int i = 0; i < BKV; ++i) {
+        for (int i = 0; i < BKV; ++i)
           if (k0 + i > key_limit) s[i] = 0xff800000u;  // -inf
-          rowmax = fmaxf(rowmax, __uint_as_float(s[i]));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < BKV; ++i) rowmax = fmaxf(rowmax, __uint_as_float(s[i]));
       }
+      // four independent chains: with two warps per sub-partition the latency has to be hidden inside the thread
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BKV; i += 8) {  // three-input max: one instruction per two elements, four chains
+        mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+      }
+      const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
       const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
       float alpha = 1.f;
@@ -247,16 +258,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         m_use = m_new;
       }
       const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
-      float rowsum = 0.f;
+      TRACE((t * 32 + j) * 8 + 3, r_in == 0 && j < 32);
+      // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(neg_mref, neg_mref);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
       uint32_t pk[BKV / 2];
 #pragma unroll
-      for (int i = 0; i < BKV; i += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_mref));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_mref));
-        rowsum += p0 + p1;
-        pk[i >> 1] = Pack2<T>::pack(p0, p1);
+      for (int i = 0; i < BKV; i += 4) {
+        const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nm2);
+        const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, nm2);
+        const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+        const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+        acc0 = __fadd2_rn(acc0, e0);
+        acc1 = __fadd2_rn(acc1, e1);
+        pk[i >> 1] = Pack2<T>::pack(e0.x, e0.y);
+        pk[(i >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
+        if (i == BKV / 2 - 4)  // first half of P is complete: start moving it while the second half is computed
+          tmem_st_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       }
-      l = l * alpha + rowsum;
+      l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
+      TRACE((t * 32 + j) * 8 + 4, r_in == 0 && j < 32);
 
       // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -270,11 +292,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           tmem_st_x32(tmem_o + c * 32, o);
         }
       }
-      tmem_st_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       tmem_st_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
+      TRACE((t * 32 + j) * 8 + 5, r_in == 0 && j < 32);
     }
 
     if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
@@ -336,6 +358,9 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.o2 = a.o2;
   p.lse2 = a.lse2;
   p.err = st->err_word;
+#ifdef TB200_TRACE
+  if (const char* tp = getenv("TB200_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(tp, nullptr, 0));
+#endif
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
