@@ -152,24 +152,24 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc(IsBf16<T>::value, false, false, BQ, BKV);
     constexpr uint32_t idesc_o = make_idesc(IsBf16<T>::value, false, true, BQ, D);
-    const uint32_t q_s = smem_u32(smem + L::kQOff);
-    const uint32_t p_s = smem_u32(smem + L::kPOff);
+    // All lanes run converged with warp-uniform operands; one elected lane issues (see common.cuh).
+    const uint64_t qd = make_smem_desc(smem_u32(smem + L::kQOff), 16, 1024);
+    const uint64_t pd = make_smem_desc(smem_u32(smem + L::kPOff), 16, 1024);
     auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j&1
-      const uint32_t k_s = smem_u32(smem + L::kKOff + (j & 1) * L::kKVBytes);
+      const uint64_t kd = make_smem_desc(smem_u32(smem + L::kKOff + (j & 1) * L::kKVBytes), 16, 1024);
       const uint32_t d_tmem = tmem_base + (j & 1) * BKV;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-        umma_ss(d_tmem, make_smem_desc(q_s + off, 16, 1024), make_smem_desc(k_s + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (BQ * 128) + (kk & 3) * 32) >> 4);
+        umma_ss_warp(d_tmem, qd + off, kd + off, idesc_s, kk > 0 ? 1u : 0u);
       }
-      umma_commit(&s_full[j & 1]);
-      umma_commit(&k_empty[j & 1]);
+      umma_commit_warp(&s_full[j & 1]);
+      umma_commit_warp(&k_empty[j & 1]);
     };
     bool ok = mbar_wait(q_full, 0, ctx, 203) && mbar_wait(&k_full[0], 0, ctx, 204);
     if (ok) {
       tc_fence_after();
-      if (lane == 0) issue_s(0);
-      __syncwarp();
+      issue_s(0);
     }
     for (int j = 0; ok && j < nt; ++j) {
       if (j + 1 < nt) {
@@ -177,24 +177,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         if (!mbar_wait(&k_full[(j + 1) & 1], n1 & 1, ctx, 205)) break;
         if (!mbar_wait(&s_empty[(j + 1) & 1], (n1 & 1) ^ 1, ctx, 206)) break;
         tc_fence_after();
-        if (lane == 0) issue_s(j + 1);
-        __syncwarp();
+        issue_s(j + 1);
       }
       if (!mbar_wait(p_ready, j & 1, ctx, 207)) break;
       if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, ctx, 208)) break;
       tc_fence_after();
-      if (lane == 0) {
-        const uint32_t v_s = smem_u32(smem + L::kVOff + (j & 1) * L::kKVBytes);
+      const uint64_t vd = make_smem_desc(smem_u32(smem + L::kVOff + (j & 1) * L::kKVBytes), BKV * 128, 1024);  // MN-major
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(p_s + (kk >> 2) * (BQ * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(v_s + kk * 2048, BKV * 128, 1024);  // MN-major: 16 keys per step
-          umma_ss(tmem_o, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&v_empty[j & 1]);
-        umma_commit(pv_done);
+      for (int kk = 0; kk < BKV / 16; ++kk) {  // 16 keys per step: +32 B in P (K-major), +2048 B in V
+        const uint64_t poff = static_cast<uint64_t>(((kk >> 2) * (BQ * 128) + (kk & 3) * 32) >> 4);
+        umma_ss_warp(tmem_o, pd + poff, vd + static_cast<uint64_t>(kk * 128), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
       }
-      __syncwarp();
+      umma_commit_warp(&v_empty[j & 1]);
+      umma_commit_warp(pv_done);
     }
   } else {
     // ------------------------------------------------------------ softmax + output (warps 2..5)

@@ -195,19 +195,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
         if (!mbar_wait(&full[stage], phase, ctx, 103)) { ok = false; break; }
         tc_fence_after();
-        if (lane == 0) {
+        {  // all lanes converged, operands warp-uniform, one elected lane issues
           const uint32_t a0 = smem_u32(smem + stage * kStageBytes);
-          const uint32_t b0 = a0 + kABytes;
+          const uint64_t ad = make_smem_desc(a0, 16, 1024);
+          const uint64_t bd = make_smem_desc(a0 + kABytes, kBChunkBytes, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t ad = make_smem_desc(a0 + k * 32, 16, 1024);            // K-major: +32 B per 16 K
-            const uint64_t bd = make_smem_desc(b0 + k * 2048, kBChunkBytes, 1024);  // MN-major: +16 K-rows
-            umma_ss(d_tmem, ad, bd, idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
-          }
-          umma_commit(&empty[stage]);                       // frees the stage when these MMAs have read it
-          if (kb == t.kb_end - 1) umma_commit(&tfull[acc]);  // accumulator complete
+          for (int k = 0; k < BK / 16; ++k)  // K-major A: +32 B per 16 K; MN-major B: +16 K-rows (2048 B); in 16-byte units
+            umma_ss_warp(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 128), idesc,
+                         (kb > t.kb_begin || k > 0) ? 1u : 0u);
+          umma_commit_warp(&empty[stage]);                       // frees the stage when these MMAs have read it
+          if (kb == t.kb_end - 1) umma_commit_warp(&tfull[acc]);  // accumulator complete
         }
-        __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       acc ^= 1;

@@ -129,18 +129,17 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
       if (!mbar_wait(&q_full[st], ph, ctx, 303)) break;
       if (!mbar_wait(&s_empty[st], ph ^ 1, ctx, 304)) break;
       tc_fence_after();
-      if (lane == 0) {
-        const uint32_t q_s = smem_u32(smem + L::kQOff + st * L::kTileBytes);
+      {  // all lanes converged, operands warp-uniform, one elected lane issues
+        const uint64_t kd = make_smem_desc(k_s, 16, 1024);
+        const uint64_t qd = make_smem_desc(smem_u32(smem + L::kQOff + st * L::kTileBytes), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-          umma_ss(tmem_base + st * BQ_, make_smem_desc(k_s + off, 16, 1024), make_smem_desc(q_s + off, 16, 1024), idesc,
-                  kk > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);
+          umma_ss_warp(tmem_base + st * BQ_, kd + off, qd + off, idesc, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[st]);
-        umma_commit(&q_empty[st]);
+        umma_commit_warp(&s_full[st]);
+        umma_commit_warp(&q_empty[st]);
       }
-      __syncwarp();
     }
   } else {
     const int quad = warp & 3;
