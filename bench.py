@@ -36,6 +36,8 @@ WORKLOADS = {
     "llama3_8b_qknorm_prefill_b8_s2048": dict(B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="qknorm"),
     "llama3_8b_prenorm_b8_s4096": dict(B=8, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="prenorm"),
     "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
+    "llama3_8b_roco_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="roco", topk=1024),
+    "llama3_8b_keyformer_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="keyformer", topk=1024),
     "llama3_8b_vanilla_prefill_b2_s2048": dict(B=2, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),   # profiling size
     "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
     # FFN blocks: M tokens, N hidden, P inner
@@ -216,26 +218,69 @@ def run_ffn(args, w, name):
         sampler.start()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
+    # The reference times CUDA-graph replays of forward() (benchmark/ffn_llama_benchmark.py:194-267): with tens of
+    # microseconds per call, Python launch overhead would otherwise be what is measured.  One graph holds one step
+    # per weight set; a step of the timed region is one replayed forward.
+    use_graph = world == 1 and M <= 1024
+    if use_graph:
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(copies):
+                    step()
+            graph.replay()
+        torch.cuda.synchronize()
+        reps = max(1, args.steps // copies)
+        with torch.cuda.stream(side):
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / (reps * copies)
+    else:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
     # stage split with the building-block GEMMs (same kernels the block chains)
     ff1 = torch.empty(M, P // world, dtype=dtype, device=dev)
-    st_ms = [0.0, 0.0]
-    for i in range(args.steps):
-        s_ = sets[i % copies]
-        a0, a1, a2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        a0.record()
+
+    def up(s_):
         ops.gemm(x, s_.w_gate, b2=s_.w_up, act=0 if gated else 1, split_k=0, out=ff1)
-        a1.record()
+
+    def down(s_):
         ops.gemm(ff1, s_.w_down, split_k=0, out=ff2)
-        a2.record()
+
+    def time_stage(fn):
+        for s_ in sets:
+            fn(s_)
         torch.cuda.synchronize()
-        st_ms[0] += a0.elapsed_time(a1) / args.steps
-        st_ms[1] += a1.elapsed_time(a2) / args.steps
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if use_graph:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g_, stream=side):
+                    for s_ in sets:
+                        fn(s_)
+                g_.replay()
+                a0.record()
+                for _ in range(reps):
+                    g_.replay()
+                a1.record()
+            torch.cuda.synchronize()
+            return a0.elapsed_time(a1) / (reps * copies)
+        a0.record()
+        for i in range(args.steps):
+            fn(sets[i % copies])
+        a1.record()
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1) / args.steps
+
+    st_ms = [time_stage(up), time_stage(down)]
     # end to end: pinned host x in, ff2 out
     x_host = host["X"].pin_memory()
     o_host = torch.empty(M, N, dtype=dtype).pin_memory()
@@ -280,7 +325,8 @@ def run_ffn(args, w, name):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": name, "tokens": M, "hidden": N, "inner": P, "act": w["act"],
                        "parallelism": "single GPU" if world == 1 else f"tensor-parallel x{world}, one NCCL all-reduce",
-                       "l2": f"{copies} rotating weight sets of {weight_bytes / 1e6:.0f} MB each (> 126 MB L2)"},
+                       "l2": f"{copies} rotating weight sets of {weight_bytes / 1e6:.0f} MB each (> 126 MB L2)",
+                       "timing": "CUDA-graph replay, as the reference harness" if use_graph else "stream launches"},
             "block_hbm_gbs": algo_bytes / world / (ms * 1e-3) / 1e9, "block_frac_of_hbm": algo_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "block_frac_of_tensor_peak": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": M * N * 2,
@@ -338,7 +384,8 @@ def main():
     dtype = torch.bfloat16
     host = make_inputs(w, dtype, seed=rank)          # every rank its own batch
     B, S, N, Hq, Hkv, D = (w[k] for k in ("B", "S", "N", "Hq", "Hkv", "D"))
-    flags = L.ATTN_CAUSAL | {"vanilla": 0, "qknorm": L.ATTN_QKNORM, "prenorm": L.ATTN_PRENORM}[w["variant"]]
+    flags = L.ATTN_CAUSAL | {"vanilla": 0, "qknorm": L.ATTN_QKNORM, "prenorm": L.ATTN_PRENORM, "roco": L.ATTN_ROCO,
+                             "keyformer": L.ATTN_KEYFORMER}[w["variant"]]
     x = host["X"].to(dev)
     wq, wk, wv = host["WQ"].to(dev), host["WK"].to(dev), host["WV"].to(dev)
     nw = host.get("norm_weight")
@@ -350,6 +397,17 @@ def main():
     kwargs = dict(past=0, head_dim=D, flags=flags, sm_scale=D ** -0.5, norm_weight=nw if flags & L.ATTN_PRENORM else None,
                   norm_eps=1e-5, q_norm_weight=qw if flags & L.ATTN_QKNORM else None,
                   k_norm_weight=kw_ if flags & L.ATTN_QKNORM else None, qk_eps=1e-6)
+    if flags & (L.ATTN_ROCO | L.ATTN_KEYFORMER):
+        topk = w.get("topk", 0)
+        kwargs.update(topk=topk, topk_idx=torch.zeros(B, Hq, topk, dtype=torch.int32, device=dev), tau=1.0)
+        if flags & L.ATTN_ROCO:
+            kwargs.update(c_out1=torch.zeros(B, Hq, S, dtype=torch.float32, device=dev),
+                          c_out2=torch.zeros(B, Hq, S, dtype=torch.float32, device=dev))
+        else:   # Gumbel(0,1) noise, generated on the device (4.3 GB at B4 S4096): -log(-log(U))
+            gen = torch.Generator(device=dev).manual_seed(rank)
+            u = torch.rand(B, Hq, S, S, generator=gen, device=dev, dtype=torch.float32).clamp_(1e-9, 1 - 1e-9)
+            kwargs.update(noise=(-torch.log(-torch.log(u))).to(dtype), c_out=torch.zeros(B, Hq, S, dtype=torch.float32, device=dev))
+            del u
 
     def step():
         ops.attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, **kwargs)
@@ -424,7 +482,8 @@ def main():
         ms, ms_e2e = tt.tolist()
 
     proj, attn = block_flops(w)
-    total = (proj + attn) * world
+    second_pass = attn / 2 if flags & (L.ATTN_ROCO | L.ATTN_KEYFORMER) else 0.0    # Q K^T recomputed for the per-key sums
+    total = (proj + attn + second_pass) * world
     peaks = load_peaks()
     if rank == 0:
         gemm_tflops = proj / (stage[1] * 1e-3) / 1e12 if stage[1] > 0 else None
@@ -440,7 +499,7 @@ def main():
             "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
                     "api": "generated-module forward(*TENSOR_PARAMS)"},
-            "gpu_launches": args.steps * (2 + (1 if flags & L.ATTN_PRENORM else 0)),
+            "gpu_launches": args.steps * (2 + (1 if flags & L.ATTN_PRENORM else 0) + (2 if flags & (L.ATTN_ROCO | L.ATTN_KEYFORMER) else 0)),
             "roofline": {"bound": "tensor", "kernel": "gemm_kernel<bf16, QKV> (tcgen05 QKV projection)",
                          "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": (gemm_tflops / peak) if gemm_tflops else None, "peak_source": peaks["source"] + " burst cuBLAS bf16",
