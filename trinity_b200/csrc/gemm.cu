@@ -2,8 +2,7 @@
 //
 // Persistent, warp-specialised kernel, one CTA per SM, 192 threads:
 //   warp 0      TMA producer: A tile (128 x 64, K-major) and four B boxes (64 K-rows x 64 columns each,
-//               MN-major because the weights are stored (K,N) row-major) into a ring of 4 stages (6 when M < 128,
-//               where only the existing A rows are fetched and the shared memory saved deepens the ring)
+//               MN-major because the weights are stored (K,N) row-major) into a 4-stage ring
 //   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16, accumulators in TMEM
 //               (two 256-column accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
 //   warps 2-5   epilogue: tcgen05.ld (thread = output row, 32 columns at a time) -> fused epilogue -> global
@@ -28,12 +27,13 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int kMaxStages = 8;
-constexpr int kABytes = BM * BK * 2;         // 16 KiB for a full 128-row tile; fewer rows are fetched when M < 128
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;         // 16 KiB
 constexpr int kBChunkBytes = BK * 64 * 2;    // 8 KiB: 64 K-rows of 64 columns
 constexpr int kBBytes = 4 * kBChunkBytes;    // 32 KiB
-constexpr int kBarrierBytes = 1024;          // barriers live in the first KiB, the ring follows (1 KiB aligned)
-constexpr int kSmemMax = 232448;             // 227 KiB opt-in limit per CTA
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kBarrierBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + slack to align the ring to 1 KiB
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
 constexpr int kTmemCols = 512;
@@ -42,10 +42,6 @@ struct GemmParams {
   CUtensorMap map_a;
   CUtensorMap map_b[3];
   int M, K, k_blocks, split_k, kb_per_split;
-  int n_stages;       // depth of the operand ring
-  int a_bytes;        // bytes of one A tile in the ring (rows actually fetched * 128, rounded up to 1 KiB)
-  int stage_bytes;    // a_bytes + 32 KiB of B
-  int stage_tx;       // bytes TMA delivers per stage (A rows fetched * 128 + 32 KiB)
   int n_src;
   int src_n[3];       // columns of each source
   int src_tile0[4];   // first column-tile of each source (prefix sums); [n_src] = number of column tiles
@@ -125,10 +121,9 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + kMaxStages;
-  uint64_t* tfull = empty + kMaxStages;
-  uint8_t* ring = smem + kBarrierBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tfull = empty + kStages;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -136,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.n_stages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -171,9 +166,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1, ctx, 101)) { ok = false; break; }
         if (lane == 0) {
-          uint8_t* sa = ring + stage * p.stage_bytes;
-          uint8_t* sb = sa + p.a_bytes;
-          mbar_arrive_expect_tx(&full[stage], p.stage_tx);
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&full[stage], kStageBytes);
           tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -183,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           }
         }
         __syncwarp();
-        if (++stage == p.n_stages) { stage = 0; phase ^= 1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -201,9 +196,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (!mbar_wait(&full[stage], phase, ctx, 103)) { ok = false; break; }
         tc_fence_after();
         {  // all lanes converged, operands warp-uniform, one elected lane issues
-          const uint32_t a0 = smem_u32(ring + stage * p.stage_bytes);
+          const uint32_t a0 = smem_u32(smem + stage * kStageBytes);
           const uint64_t ad = make_smem_desc(a0, 16, 1024);
-          const uint64_t bd = make_smem_desc(a0 + p.a_bytes, kBChunkBytes, 1024);
+          const uint64_t bd = make_smem_desc(a0 + kABytes, kBChunkBytes, 1024);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)  // K-major A: +32 B per 16 K; MN-major B: +16 K-rows (2048 B); in 16-byte units
             umma_ss_warp(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 128), idesc,
@@ -211,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           umma_commit_warp(&empty[stage]);                       // frees the stage when these MMAs have read it
           if (kb == t.kb_end - 1) umma_commit_warp(&tfull[acc]);  // accumulator complete
         }
-        if (++stage == p.n_stages) { stage = 0; phase ^= 1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -420,31 +415,17 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
   }
 }
 
-// Ring geometry.  With fewer than 128 rows only the rows that exist are fetched (the MMA still runs 128 rows; the
-// rest of the A tile is stale shared memory whose products land in accumulator rows that are never stored), and
-// the shared memory saved buys a deeper ring -- what a weight-streaming (HBM-bound) call needs.
-// Returns the number of A rows one TMA box fetches.
-int plan_ring(GemmParams* p, int M) {
-  const int rows = M >= BM ? BM : (M + 7) / 8 * 8;
-  p->a_bytes = (rows * 128 + 1023) / 1024 * 1024;
-  p->stage_bytes = p->a_bytes + kBBytes;
-  p->stage_tx = rows * 128 + kBBytes;
-  int n = (kSmemMax - kBarrierBytes - 1024) / p->stage_bytes;
-  p->n_stages = n > kMaxStages ? kMaxStages : n;
-  return rows;
-}
-
 template <typename T, int MODE>
 int launch_mode(const GemmParams& p, int grid, cudaStream_t stream) {
   static bool attr_set[32] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(gemm_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  gemm_kernel<T, MODE><<<grid, kThreads, kBarrierBytes + p.n_stages * p.stage_bytes + 1024, stream>>>(p);
+  gemm_kernel<T, MODE><<<grid, kThreads, kSmemBytes, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
@@ -535,7 +516,7 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(g.K) * 2};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(plan_ring(&p, g.M))};
+    const uint32_t box[2] = {BK, BM};
     if ((status = make_tensor_map(&p.map_a, g.A, 2, dims, strides, box)) != TB200_OK) return status;
   }
   for (int s = 0; s < g.n_src; ++s) {
@@ -665,7 +646,7 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(plan_ring(&p, M))};
+    const uint32_t box[2] = {BK, BM};
     if ((status = make_tensor_map(&p.map_a, a->a, 2, dims, strides, box)) != TB200_OK) return status;
   }
   const void* srcs[2] = {a->b, a->b2};
