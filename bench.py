@@ -38,6 +38,7 @@ WORKLOADS = {
     "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
     "llama3_8b_roco_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="roco", topk=1024),
     "llama3_8b_keyformer_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="keyformer", topk=1024),
+    "llama3_8b_keyformer_b1_s4096": dict(B=1, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="keyformer", topk=1024),   # profiling size
     "llama3_8b_vanilla_prefill_b2_s2048": dict(B=2, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),   # profiling size
     "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
     # FFN blocks: M tokens, N hidden, P inner

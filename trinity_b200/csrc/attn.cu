@@ -31,15 +31,19 @@ constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
-template <int D> struct AttnSmem {
+// With a noise tensor (KeyFormer) the K and V rings shrink to one stage each -- that pass is bound by its two
+// exponentials per score, not by the loads -- and the room goes to a two-deep ring of noise tiles.
+template <int D, bool NOISE> struct AttnSmem {
+  static constexpr int kKVStages = NOISE ? 1 : 2;
   static constexpr int kQBytes = BQ * D * 2;
   static constexpr int kKVBytes = BKV * D * 2;
   static constexpr int kPBytes = BQ * BKV * 2;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQBytes;
-  static constexpr int kVOff = kKOff + 2 * kKVBytes;
-  static constexpr int kPOff = kVOff + 2 * kKVBytes;
-  static constexpr int kBarOff = kPOff + kPBytes;
+  static constexpr int kVOff = kKOff + kKVStages * kKVBytes;
+  static constexpr int kPOff = kVOff + kKVStages * kKVBytes;
+  static constexpr int kNoiseOff = kPOff + kPBytes;             // [2][2 chunks of 64 keys][128 rows][128 B], swizzled
+  static constexpr int kBarOff = kNoiseOff + (NOISE ? 2 * kPBytes : 0);
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
@@ -47,6 +51,8 @@ struct AttnParams {
   CUtensorMap map_q;  // dims {D, S, B*Hq}
   CUtensorMap map_k;  // dims {D, past+S, B*Hkv}, pitch cache_len*D
   CUtensorMap map_v;
+  CUtensorMap map_noise;  // dims {past+S, S, B*Hq}; valid when noise_tma
+  int noise_tma;          // the noise rows are 16-byte aligned: tiles come through TMA, else plain loads
   int B, S, Hq, Hkv, past, kv_len, causal;
   float scale_log2;   // sm_scale * log2(e)
   float inv_tau;
@@ -59,7 +65,8 @@ struct AttnParams {
 
 template <typename T, int D, bool NOISE>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnParams p) {
-  using L = AttnSmem<D>;
+  using L = AttnSmem<D, NOISE>;
+  constexpr int KVS = L::kKVStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -72,7 +79,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   uint64_t* s_empty = bars + 11; // [2]
   uint64_t* p_ready = bars + 13;
   uint64_t* pv_done = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* n_full = bars + 15;   // [2] noise tiles
+  uint64_t* n_empty = bars + 17;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -97,6 +106,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 128);
+      mbar_init(&n_full[i], 1);
+      mbar_init(&n_empty[i], 128);
     }
     mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
@@ -129,8 +140,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     }
     __syncwarp();
     for (int j = 0; j < nt; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
+      const int st = j % KVS;
+      const uint32_t ph = (j / KVS) & 1;
+      if (NOISE && p.noise_tma) {
+        if (!mbar_wait(&n_empty[j & 1], ((j >> 1) & 1) ^ 1, ctx, 212)) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&n_full[j & 1], L::kPBytes);
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc)
+            tma_load_3d(smem + L::kNoiseOff + (j & 1) * L::kPBytes + kc * (BQ * 128), &p.map_noise, &n_full[j & 1], j * BKV + kc * 64, q0,
+                        b * p.Hq + hq);
+        }
+        __syncwarp();
+      }
       if (!mbar_wait(&k_empty[st], ph ^ 1, ctx, 201)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&k_full[st], L::kKVBytes);
@@ -156,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     const uint64_t qd = make_smem_desc(smem_u32(smem + L::kQOff), 16, 1024);
     const uint64_t pd = make_smem_desc(smem_u32(smem + L::kPOff), 16, 1024);
     auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j&1
-      const uint64_t kd = make_smem_desc(smem_u32(smem + L::kKOff + (j & 1) * L::kKVBytes), 16, 1024);
+      const uint64_t kd = make_smem_desc(smem_u32(smem + L::kKOff + (j % KVS) * L::kKVBytes), 16, 1024);
       const uint32_t d_tmem = tmem_base + (j & 1) * BKV;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -164,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         umma_ss_warp(d_tmem, qd + off, kd + off, idesc_s, kk > 0 ? 1u : 0u);
       }
       umma_commit_warp(&s_full[j & 1]);
-      umma_commit_warp(&k_empty[j & 1]);
+      umma_commit_warp(&k_empty[j % KVS]);
     };
     bool ok = mbar_wait(q_full, 0, ctx, 203) && mbar_wait(&k_full[0], 0, ctx, 204);
     if (ok) {
@@ -174,21 +196,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     for (int j = 0; ok && j < nt; ++j) {
       if (j + 1 < nt) {
         const int n1 = (j + 1) >> 1;
-        if (!mbar_wait(&k_full[(j + 1) & 1], n1 & 1, ctx, 205)) break;
+        if (!mbar_wait(&k_full[(j + 1) % KVS], ((j + 1) / KVS) & 1, ctx, 205)) break;
         if (!mbar_wait(&s_empty[(j + 1) & 1], (n1 & 1) ^ 1, ctx, 206)) break;
         tc_fence_after();
         issue_s(j + 1);
       }
       if (!mbar_wait(p_ready, j & 1, ctx, 207)) break;
-      if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, ctx, 208)) break;
+      if (!mbar_wait(&v_full[j % KVS], (j / KVS) & 1, ctx, 208)) break;
       tc_fence_after();
-      const uint64_t vd = make_smem_desc(smem_u32(smem + L::kVOff + (j & 1) * L::kKVBytes), BKV * 128, 1024);  // MN-major
+      const uint64_t vd = make_smem_desc(smem_u32(smem + L::kVOff + (j % KVS) * L::kKVBytes), BKV * 128, 1024);  // MN-major
 #pragma unroll
       for (int kk = 0; kk < BKV / 16; ++kk) {  // 16 keys per step: +32 B in P (K-major), +2048 B in V
         const uint64_t poff = static_cast<uint64_t>(((kk >> 2) * (BQ * 128) + (kk & 3) * 32) >> 4);
         umma_ss_warp(tmem_o, pd + poff, vd + static_cast<uint64_t>(kk * 128), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
       }
-      umma_commit_warp(&v_empty[j & 1]);
+      umma_commit_warp(&v_empty[j % KVS]);
       umma_commit_warp(pv_done);
     }
   } else {
@@ -232,45 +254,50 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         s[i] = __float_as_uint(t);
         rowmax = fmaxf(rowmax, t);
       }
-      if (NOISE) {  // online log-sum-exp of (scale*s + noise)/tau, log2 domain
-        float tmax = -INFINITY;
-        // two sweeps over the noise row keep registers bounded: max first, then the sum
-        for (int sweep = 0; sweep < 2; ++sweep) {
-          float acc = 0.f;
-          const float mref = (sweep == 1) ? fmaxf(mt, tmax) : 0.f;
+      if (NOISE) {  // log-sum-exp of x = (scale*s + noise)/tau in the log2 domain, one sweep over the noise row:
+        // the exponent reference mt only has to keep exp2(x - mt) inside fp32 range, so it is moved after the sweep
+        // and only when the row's maximum ran more than 2^60 ahead of it; it starts at the noise-free row maximum.
+        const uint8_t* n_smem = smem + L::kNoiseOff + (j & 1) * L::kPBytes;
+        if (p.noise_tma) {
+          if (!mbar_wait(&n_full[j & 1], (j >> 1) & 1, ctx, 213)) { ok = false; break; }
+        }
+        if (mt == -INFINITY && rowmax > -INFINITY) mt = rowmax * p.inv_tau;
+        const float nscale = kLog2e * p.inv_tau;
+        const float neg_ref = (mt == -INFINITY) ? 0.f : -mt;
+        float tmax = -INFINITY, acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-          for (int u = 0; u < BKV / 8; ++u) {
-            float nz[8];
-            const int kbase = k0 + u * 8;
-            if (row_ok && kbase + 7 < p.kv_len && ((p.kv_len & 7) == 0)) {
-              const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(noise_row + kbase));
-              const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
+        for (int u = 0; u < BKV / 8; ++u) {
+          float nz[8];
+          const int kbase = k0 + u * 8;
+          if (p.noise_tma) {  // row r_in of the swizzled tile: 16-byte unit u lands at (u & 7) ^ (row & 7) of its 64-key chunk
+            const uint4 q4 = *reinterpret_cast<const uint4*>(n_smem + (u >> 3) * (BQ * 128) + r_in * 128 + (((u & 7) ^ (r_in & 7)) << 4));
+            const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f2 = Pack2<T>::unpack(w[e]);
-                nz[2 * e] = f2.x;
-                nz[2 * e + 1] = f2.y;
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                nz[e] = (row_ok && kbase + e < p.kv_len) ? static_cast<float>(noise_row[kbase + e]) : 0.f;
+            for (int e = 0; e < 4; ++e) {
+              const float2 f2 = Pack2<T>::unpack(w[e]);
+              nz[2 * e] = f2.x;
+              nz[2 * e + 1] = f2.y;
             }
+          } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float x = (__uint_as_float(s[u * 8 + e]) + nz[e] * kLog2e) * p.inv_tau;  // -inf stays -inf
-              if (sweep == 0) tmax = fmaxf(tmax, x);
-              else acc += fast_exp2(x - mref);
-            }
+            for (int e = 0; e < 8; ++e)
+              nz[e] = (row_ok && kbase + e < p.kv_len) ? static_cast<float>(noise_row[kbase + e]) : 0.f;
           }
-          if (sweep == 1) {
-            const float mnew = fmaxf(mt, tmax);
-            if (mnew > -INFINITY) {
-              lt = lt * fast_exp2(mt - mnew) + acc;
-              mt = mnew;
-            }
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float x0 = fmaf(nz[e], nscale, fmaf(__uint_as_float(s[u * 8 + e]), p.inv_tau, neg_ref));  // -inf stays -inf
+            const float x1 = fmaf(nz[e + 1], nscale, fmaf(__uint_as_float(s[u * 8 + e + 1]), p.inv_tau, neg_ref));
+            tmax = max3(tmax, x0, x1);
+            acc0 += fast_exp2(x0);
+            acc1 += fast_exp2(x1);
           }
         }
+        lt += acc0 + acc1;
+        if (tmax > 60.f) {  // move the reference up to this row maximum
+          lt *= fast_exp2(-tmax);
+          mt += tmax;
+        }
+        if (p.noise_tma) mbar_arrive(&n_empty[j & 1]);
       }
 
       const float m_new = fmaxf(m_use, rowmax);
@@ -362,11 +389,11 @@ int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel<T, D, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<D>::kTotal) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_fwd_kernel<T, D, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<D, NOISE>::kTotal) != cudaSuccess)
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  attn_fwd_kernel<T, D, NOISE><<<grid, kThreads, AttnSmem<D>::kTotal, stream>>>(p);
+  attn_fwd_kernel<T, D, NOISE><<<grid, kThreads, AttnSmem<D, NOISE>::kTotal, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
@@ -419,6 +446,13 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
     const uint32_t box[3] = {64, BKV, 1};
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
     if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
+  }
+  if (a.noise != nullptr && (p.kv_len & 7) == 0) {  // rows of the noise tensor are 16-byte aligned: tiles by TMA
+    const uint64_t dims[3] = {static_cast<uint64_t>(p.kv_len), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
+    const uint64_t strides[2] = {static_cast<uint64_t>(p.kv_len) * 2, static_cast<uint64_t>(a.S) * p.kv_len * 2};
+    const uint32_t box[3] = {64, BQ, 1};
+    if ((status = make_tensor_map(&p.map_noise, a.noise, 3, dims, strides, box)) != TB200_OK) return status;
+    p.noise_tma = 1;
   }
   const dim3 grid((a.S + BQ - 1) / BQ, a.Hq, a.B);
   const bool noise = a.noise != nullptr;

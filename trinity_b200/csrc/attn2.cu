@@ -1,6 +1,6 @@
 // Attention forward, two query tiles per CTA ("ping-pong"): the kernel used when no noise tensor is involved.
 //
-// One CTA per (256 queries, q head, batch element), 320 threads:
+// One CTA per (256 queries, q head, batch element), 320 threads (kHalves = 1):
 //   warp 0      TMA producer: both Q tiles once, then K and V tiles of 128 keys through two-deep rings
 //   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}
 //   warps 2-5   softmax of query tile 0          warps 6-9   softmax of query tile 1
@@ -24,7 +24,10 @@ namespace {
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kThreads = 320;
+// Threads per query row in the softmax.  2 was measured slower on B200 (0.418 ms against 0.353 ms on the Llama-3-8B
+// B8 S2048 prefill): the row-max exchange and the 96-register cap of a 576-thread CTA cost more than the extra warps hide.
+constexpr int kHalves = 1;
+constexpr int kThreads = 64 + 2 * 128 * kHalves;  // TMA warp, MMA warp, softmax warps of two query tiles
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;
@@ -35,7 +38,8 @@ template <int D> struct Smem2 {
   static constexpr int kKOff = 2 * kTile;         // two stages
   static constexpr int kVOff = 4 * kTile;         // two stages
   static constexpr int kBarOff = 6 * kTile;
-  static constexpr int kTotal = kBarOff + 256 + 1024;
+  static constexpr int kXchOff = kBarOff + 256;   // row max / row sum exchange between the threads of a row
+  static constexpr int kTotal = kXchOff + 6 * 1024 + 1024;
 };
 
 struct Attn2Params {
@@ -68,7 +72,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   uint64_t* s_full = bars + 9;    // [2] per query tile
   uint64_t* p_ready = bars + 11;  // [2] per query tile
   uint64_t* pv_done = bars + 13;  // [2] per query tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* row_xch = bars + 15;  // [2] per query tile: the threads of a row have published their partial
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -96,8 +101,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 128 * kHalves);
       mbar_init(&pv_done[i], 1);
+      mbar_init(&row_xch[i], 128 * kHalves);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -207,49 +213,62 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       if (ok && j + 1 < nt_max) umma_commit_warp(&k_empty[(j + 1) & 1]);
     }
   } else {
-    // ------------------------------------------------------------ softmax warpgroups
-    const int t = (warp - 2) >> 2;  // query tile of this warpgroup
+    // ------------------------------------------------------------ softmax warps
+    // kHalves threads share a query row: thread (row, h) owns the S columns [h*CW, (h+1)*CW) of the row and the O
+    // columns [h*D/kHalves, ...).  The two threads sit in different warps that may touch the same TMEM lanes
+    // (warp % 4 is equal), which doubles the warps per SM sub-partition available to hide MUFU / FMA latency.
+    constexpr int CW = BKV / kHalves;   // S columns per thread
+    constexpr int OW = D / kHalves;     // O columns per thread
+    const int sw = warp - 2;
+    const int t = sw / (4 * kHalves);   // query tile
+    const int h = (sw >> 2) % kHalves;  // column half
     const int quad = warp & 3;
     const int r_in = quad * 32 + lane;
     const int qi = q0 + t * BQ + r_in;
     const bool row_ok = qi < p.S;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * BKV + lane_sel;
-    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
+    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + h * OW + lane_sel;
     const int key_limit = p.causal ? min(p.past + qi, p.kv_len - 1) : p.kv_len - 1;
     const int my_nt = nt[t];
+    float* xmax = reinterpret_cast<float*>(smem + L::kXchOff) + t * (2 * kHalves * 128);  // [parity][half][row]
+    float* xsum = reinterpret_cast<float*>(smem + L::kXchOff) + 2 * (2 * kHalves * 128) + t * (kHalves * 128);
     float m_use = -INFINITY, l = 0.f;
     bool ok = true;
 
     for (int j = 0; j < my_nt; ++j) {
-      const int k0 = j * BKV;
-      TRACE((t * 32 + j) * 8 + 0, r_in == 0 && j < 32);
+      const int k0 = j * BKV + h * CW;
+      TRACE((t * 32 + j) * 8 + 0, r_in == 0 && h == 0 && j < 32);
       if (!mbar_wait(&s_full[t], j & 1, ctx, 408)) { ok = false; break; }
       tc_fence_after();
-      TRACE((t * 32 + j) * 8 + 1, r_in == 0 && j < 32);
-      uint32_t s[BKV];
-      tmem_ld_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_ld_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_ld_x32(tmem_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-      tmem_ld_x32(tmem_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
-      tmem_wait_ld();
-      TRACE((t * 32 + j) * 8 + 2, r_in == 0 && j < 32);
-
-      if (k0 + BKV - 1 > key_limit) {  // tile touches the causal diagonal or the end of the keys
+      TRACE((t * 32 + j) * 8 + 1, r_in == 0 && h == 0 && j < 32);
+      uint32_t s[CW];
 #pragma unroll
-        for (int i = 0; i < BKV; ++i)
+      for (int c = 0; c < CW / 32; ++c) tmem_ld_x32(tmem_s + h * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      tmem_wait_ld();
+      TRACE((t * 32 + j) * 8 + 2, r_in == 0 && h == 0 && j < 32);
+
+      if (k0 + CW - 1 > key_limit) {  // these columns touch the causal diagonal or the end of the keys
+#pragma unroll
+        for (int i = 0; i < CW; ++i)
           if (k0 + i > key_limit) s[i] = 0xff800000u;  // -inf
       }
-      // four independent chains: with two warps per sub-partition the latency has to be hidden inside the thread
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BKV; i += 8) {  // three-input max: one instruction per two elements, four chains
+      for (int i = 0; i < CW; i += 8) {  // three-input max: one instruction per two elements, four chains
         mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
         mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
         mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
         mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
       }
-      const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      if (kHalves > 1) {  // combine with the other half of the row (bounded wait, no bar.sync)
+        float* slot = xmax + (j & 1) * (kHalves * 128);
+        slot[h * 128 + r_in] = rowmax;
+        mbar_arrive(&row_xch[t]);
+        if (!mbar_wait(&row_xch[t], j & 1, ctx, 410)) { ok = false; break; }
+        rowmax = fmaxf(rowmax, slot[(h ^ 1) * 128 + r_in]);
+      }
       const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
       const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
       float alpha = 1.f;
@@ -258,14 +277,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         m_use = m_new;
       }
       const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
-      TRACE((t * 32 + j) * 8 + 3, r_in == 0 && j < 32);
+      TRACE((t * 32 + j) * 8 + 3, r_in == 0 && h == 0 && j < 32);
       // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nm2 = make_float2(neg_mref, neg_mref);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-      uint32_t pk[BKV / 2];
+      uint32_t pk[CW / 2];
 #pragma unroll
-      for (int i = 0; i < BKV; i += 4) {
+      for (int i = 0; i < CW; i += 4) {
         const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nm2);
         const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, nm2);
         const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
@@ -274,17 +293,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         acc1 = __fadd2_rn(acc1, e1);
         pk[i >> 1] = Pack2<T>::pack(e0.x, e0.y);
         pk[(i >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
-        if (i == BKV / 2 - 4)  // first half of P is complete: start moving it while the second half is computed
-          tmem_st_x32(tmem_s + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       }
-      l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
-      TRACE((t * 32 + j) * 8 + 4, r_in == 0 && j < 32);
+      l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));  // this thread's share of the row sum
+      TRACE((t * 32 + j) * 8 + 4, r_in == 0 && h == 0 && j < 32);
 
       // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         uint32_t o[32];
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < OW / 32; ++c) {
           tmem_ld_x32(tmem_o + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
@@ -292,20 +309,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           tmem_st_x32(tmem_o + c * 32, o);
         }
       }
-      tmem_st_x32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+#pragma unroll
+      for (int c = 0; c < CW / 64; ++c)  // 64 keys = 32 packed columns per store
+        tmem_st_x32(tmem_s + h * (CW / 2) + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[c * 32]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
-      TRACE((t * 32 + j) * 8 + 5, r_in == 0 && j < 32);
+      TRACE((t * 32 + j) * 8 + 5, r_in == 0 && h == 0 && j < 32);
     }
 
+    if (ok && my_nt > 0 && kHalves > 1) {  // total row sum
+      xsum[h * 128 + r_in] = l;
+      mbar_arrive(&row_xch[t]);
+      ok = mbar_wait(&row_xch[t], my_nt & 1, ctx, 411);
+      if (ok) l += xsum[(h ^ 1) * 128 + r_in];
+    }
     if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
       tc_fence_after();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(b) * p.S + qi) * p.Hq + hq) * D;
+      T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(b) * p.S + qi) * p.Hq + hq) * D + h * OW;
       uint32_t o[32];
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OW / 32; ++c) {
         tmem_ld_x32(tmem_o + c * 32, o);
         tmem_wait_ld();
         if (row_ok) {
@@ -318,7 +343,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
                               Pack2<T>::pack(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l));
         }
       }
-      if (row_ok && p.lse2 != nullptr) p.lse2[(static_cast<long long>(b) * p.Hq + hq) * p.S + qi] = m_use + log2f(l);
+      if (row_ok && h == 0 && p.lse2 != nullptr) p.lse2[(static_cast<long long>(b) * p.Hq + hq) * p.S + qi] = m_use + log2f(l);
     }
   }
 

@@ -26,11 +26,13 @@ constexpr int kThreads = 192;
 constexpr int kTmemCols = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int D> struct ScoreSmem {
+template <int D, bool NOISE> struct ScoreSmem {
   static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kNoiseBytes = 128 * 128 * 2;              // [2 chunks of 64 keys][128 queries][128 B], swizzled
   static constexpr int kKOff = 0;
   static constexpr int kQOff = kTileBytes;
-  static constexpr int kLseOff = kQOff + 2 * kTileBytes;       // [2 buffers][2 statistics][128] fp32
+  static constexpr int kNoiseOff = kQOff + 2 * kTileBytes;       // two-deep ring (KeyFormer only)
+  static constexpr int kLseOff = kNoiseOff + (NOISE ? 2 * kNoiseBytes : 0);  // [2 buffers][2 statistics][128] fp32
   static constexpr int kBarOff = kLseOff + 2 * 2 * 128 * 4;
   static constexpr int kTotal = kBarOff + 128 + 1024;
 };
@@ -38,6 +40,8 @@ template <int D> struct ScoreSmem {
 struct ScoreParams {
   CUtensorMap map_q;
   CUtensorMap map_k;
+  CUtensorMap map_noise;  // dims {past+S, S, B*Hq}; valid when noise_tma
+  int noise_tma;
   int B, S, Hq, Hkv, past, kv_len, causal;
   float scale_log2, inv_tau;
   const float* lse2;
@@ -53,7 +57,7 @@ __device__ __forceinline__ void bar_sync_reducers() { asm volatile("bar.sync 1, 
 
 template <typename T, int D, bool NOISE>
 __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constant__ ScoreParams p) {
-  using L = ScoreSmem<D>;
+  using L = ScoreSmem<D, NOISE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -62,7 +66,9 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
   uint64_t* q_empty = bars + 3;  // [2]
   uint64_t* s_full = bars + 5;   // [2]
   uint64_t* s_empty = bars + 7;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* n_full = bars + 9;   // [2] noise tiles
+  uint64_t* n_empty = bars + 11; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* lse_s = reinterpret_cast<float*>(smem + L::kLseOff);
 
@@ -85,6 +91,8 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
       mbar_init(&q_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 128);
+      mbar_init(&n_full[i], 1);
+      mbar_init(&n_empty[i], 128);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -109,6 +117,17 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
     __syncwarp();
     for (int i = 0; i < nt; ++i) {
       const int st = i & 1;
+      if (NOISE && p.noise_tma) {
+        if (!mbar_wait(&n_empty[st], ((i >> 1) & 1) ^ 1, ctx, 306)) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&n_full[st], L::kNoiseBytes);
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc)
+            tma_load_3d(smem + L::kNoiseOff + st * L::kNoiseBytes + kc * (128 * 128), &p.map_noise, &n_full[st], k0 + kc * 64,
+                        (first_tile + i) * BQ_, b * p.Hq + hq);
+        }
+        __syncwarp();
+      }
       if (!mbar_wait(&q_empty[st], ((i >> 1) & 1) ^ 1, ctx, 301)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&q_full[st], L::kTileBytes);
@@ -161,6 +180,13 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
       bar_sync_reducers();
       if (!mbar_wait(&s_full[st], (i >> 1) & 1, ctx, 305)) break;
       tc_fence_after();
+      if (NOISE && p.noise_tma) {
+        if (!mbar_wait(&n_full[st], (i >> 1) & 1, ctx, 307)) break;
+      }
+      // this key's column of the swizzled noise tile: element (query c, key r_in)
+      const uint8_t* n_col = smem + L::kNoiseOff + st * L::kNoiseBytes + (r_in >> 6) * (128 * 128) + (r_in & 7) * 2;
+      const int n_unit = (r_in & 63) >> 3;
+      const float nscale = kLog2e * p.inv_tau;
       const float* lse_q = lse_s + (st * 2 + 0) * 128;
       const float* lse_t = lse_s + (st * 2 + 1) * 128;
       // a query column c is visible to this key iff kj <= past + q0 + c
@@ -175,20 +201,24 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
           const int c = cc * 32 + e;
           const bool vis = key_ok && (c >= c_min);
           const float t = __uint_as_float(s[e]) * p.scale_log2;
-          const float pr = vis ? fast_exp2(t - lse_q[c]) : 0.f;
-          acc_p += pr;
-          acc_p2 = fmaf(pr, pr, acc_p2);
-          if (NOISE) {
+          if (!NOISE) {  // RoCo: sums of p and p^2
+            const float pr = vis ? fast_exp2(t - lse_q[c]) : 0.f;
+            acc_p += pr;
+            acc_p2 = fmaf(pr, pr, acc_p2);
+          } else {       // KeyFormer: only the perturbed probability is summed
             float nz = 0.f;
-            if (vis && (q0 + c) < p.S)
+            if (p.noise_tma)
+              nz = static_cast<float>(*reinterpret_cast<const T*>(n_col + c * 128 + ((n_unit ^ (c & 7)) << 4)));
+            else if (vis && (q0 + c) < p.S)
               nz = static_cast<float>(static_cast<const T*>(p.noise)[(head_row0 + q0 + c) * p.kv_len + kj]);
-            const float pt = vis ? fast_exp2((t + nz * kLog2e) * p.inv_tau - lse_t[c]) : 0.f;
+            const float pt = vis ? fast_exp2(fmaf(nz, nscale, fmaf(t, p.inv_tau, -lse_t[c]))) : 0.f;
             acc_pt += pt;
           }
         }
       }
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
+      if (NOISE && p.noise_tma) mbar_arrive(&n_empty[st]);
     }
     if (key_ok) {
       const long long o = (static_cast<long long>(b) * p.Hq + hq) * p.kv_len + kj;
@@ -212,11 +242,11 @@ int launch_one(const ScoreParams& p, dim3 grid, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(score_kernel<T, D, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ScoreSmem<D>::kTotal) != cudaSuccess)
+    if (cudaFuncSetAttribute(score_kernel<T, D, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ScoreSmem<D, NOISE>::kTotal) != cudaSuccess)
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  score_kernel<T, D, NOISE><<<grid, kThreads, ScoreSmem<D>::kTotal, stream>>>(p);
+  score_kernel<T, D, NOISE><<<grid, kThreads, ScoreSmem<D, NOISE>::kTotal, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
@@ -266,6 +296,13 @@ int launch_score_colreduce(const ScoreLaunch& a, cudaStream_t stream) {
     const uint64_t strides[2] = {D * 2, static_cast<uint64_t>(a.cache_len) * D * 2};
     const uint32_t box[3] = {64, 128, 1};
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
+  }
+  if (noise && (p.kv_len & 7) == 0) {  // rows of the noise tensor are 16-byte aligned: tiles by TMA
+    const uint64_t dims[3] = {static_cast<uint64_t>(p.kv_len), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
+    const uint64_t strides[2] = {static_cast<uint64_t>(p.kv_len) * 2, static_cast<uint64_t>(a.S) * p.kv_len * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    if ((status = make_tensor_map(&p.map_noise, a.noise, 3, dims, strides, box)) != TB200_OK) return status;
+    p.noise_tma = 1;
   }
   const dim3 grid((p.kv_len + BK_ - 1) / BK_, a.Hq, a.B);
   if (a.dtype == TB200_BF16) return launch_t<__nv_bfloat16>(p, a.D, noise, grid, stream);
