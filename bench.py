@@ -356,6 +356,9 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
+                    help="attention at N > 1 GPUs: 'batch' = every rank its own batch (weak scaling), 'heads' = one batch, "
+                         "KV-head groups dealt out over the ranks (strong scaling)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if w.get("kind") == "ffn":
@@ -383,8 +386,13 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     dtype = torch.bfloat16
-    host = make_inputs(w, dtype, seed=rank)          # every rank its own batch
+    head_sharded = args.shard == "heads" and world > 1
+    host = make_inputs(w, dtype, seed=0 if head_sharded else rank)   # batch-sharded: every rank its own batch
     B, S, N, Hq, Hkv, D = (w[k] for k in ("B", "S", "N", "Hq", "Hkv", "D"))
+    if head_sharded:   # KV-head groups: x replicated, column slices of the weights, O2 comes out column-sharded
+        from trinity_b200 import shard
+        host["WQ"], host["WK"], host["WV"] = shard.shard_attention_weights(host["WQ"], host["WK"], host["WV"], D, rank, world)
+        Hq, Hkv = Hq // world, Hkv // world
     flags = L.ATTN_CAUSAL | {"vanilla": 0, "qknorm": L.ATTN_QKNORM, "prenorm": L.ATTN_PRENORM, "roco": L.ATTN_ROCO,
                              "keyformer": L.ATTN_KEYFORMER}[w["variant"]]
     x = host["X"].to(dev)
@@ -509,18 +517,20 @@ def main():
 
     proj, attn = block_flops(w)
     second_pass = attn / 2 if flags & (L.ATTN_ROCO | L.ATTN_KEYFORMER) else 0.0    # Q K^T recomputed for the per-key sums
-    total = (proj + attn + second_pass) * world
+    total = (proj + attn + second_pass) * (1 if head_sharded else world)
     peaks = load_peaks()
     if rank == 0:
-        gemm_tflops = proj / (stage[1] * 1e-3) / 1e12 if stage[1] > 0 else None
-        attn_tflops = attn / (stage[2] * 1e-3) / 1e12 if stage[2] > 0 else None
+        share = world if head_sharded else 1          # this rank's part of the block's work
+        gemm_tflops = proj / share / (stage[1] * 1e-3) / 1e12 if stage[1] > 0 else None
+        attn_tflops = attn / share / (stage[2] * 1e-3) / 1e12 if stage[2] > 0 else None
         peak = peaks["bf16_tflops"]
         line = {
             "metric": "fused_block_tflops", "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "us_per_call": ms * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if head_sharded else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": B, "seq_len": S, "hidden": N, "q_heads": Hq, "kv_heads": Hkv,
-                       "head_dim": D, "causal": True, "parallelism": f"batch-sharded x{world}, no collective",
+                       "head_dim": D, "causal": True, "parallelism": (f"KV-head groups over {world} GPUs, no collective" if head_sharded else f"batch-sharded x{world}, no collective"),
                        "l2": "working set (x, weights, q, caches, o2 > 400 MB) exceeds the 126 MB L2"},
             "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": o_host[0].numel() * 2,
@@ -529,7 +539,7 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "gemm_kernel<bf16, QKV> (tcgen05 QKV projection)",
                          "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": (gemm_tflops / peak) if gemm_tflops else None, "peak_source": peaks["source"] + " burst cuBLAS bf16",
-                         "traffic": None, "flops_per_launch": proj, "ms_per_launch": stage[1]},
+                         "traffic": None, "flops_per_launch": proj / share, "ms_per_launch": stage[1]},
             "stages": {"rmsnorm_ms": stage[0], "qkv_gemm_ms": stage[1], "attention_ms": stage[2], "scores_ms": stage[3],
                        "qkv_gemm_tflops": gemm_tflops, "attention_tflops": attn_tflops,
                        "attention_frac_of_peak": (attn_tflops / peak) if attn_tflops else None},
