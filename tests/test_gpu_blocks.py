@@ -130,8 +130,11 @@ def test_small_golden_through_generated_module(golden_dir, tag):
 
 @pytest.mark.parametrize("model", ["llama", "falcon"])
 def test_reference_shapes_against_golden(golden_dir, model):
-    """The reference's own shapes (M16, P1024; Llama N4096 D128, Falcon N4544 D64), its input distribution
-    (seed 42, randn*0.01, fp16) and its own tolerance on O2 (convert_eval_rms.py:387: rtol 1e-2, atol 2e-3)."""
+    """The reference's own shapes (M16, P1024; Llama N4096 D128, Falcon N4544 D64) and its input distribution (seed 42,
+    randn*0.01, fp16).  Tolerance: rtol 2e-2 with atol 2e-2 of the output's range -- the 16-bit-vs-fp32 bound, scaled
+    because the un-normalised variants produce outputs of magnitude 0.006 at this input scale, for which the
+    reference's own absolute 2e-3 (convert_eval_rms.py:387) would accept anything, while the PreNorm variants produce
+    O(1) outputs for which the reference's own Triton path misses that same 2e-3."""
     from tests.golden.make_golden import fingerprint
     z = np.load(os.path.join(golden_dir, f"refshape_attn_{model}.npz"))
     M, N, D, P = (int(v) for v in z["shape"])
@@ -151,10 +154,12 @@ def test_reference_shapes_against_golden(golden_dir, model):
                          c_out=aux["c_out"] if flags & KF else None, c_out1=aux["c_out1"] if flags & RC else None,
                          c_out2=aux["c_out2"] if flags & RC else None)
         ops.device_status()
-        close(o2, torch.from_numpy(z[f"{cls}.O2"]), rtol=1e-2, atol=2e-3, msg=f"{cls}.O2")
+        want = torch.from_numpy(z[f"{cls}.O2"])
+        close(o2, want, rtol=2e-2, atol=2e-2 * float(want.abs().max()), msg=f"{cls}.O2")
         for name, key in (("C_out", "c_out"), ("C_out1", "c_out1"), ("C_out2", "c_out2")):
             if f"{cls}.{name}" in z.files:
-                close(aux[key], torch.from_numpy(z[f"{cls}.{name}"]), rtol=1e-2, atol=2e-3, msg=f"{cls}.{name}")
+                want = torch.from_numpy(z[f"{cls}.{name}"])
+                close(aux[key], want, rtol=2e-2, atol=2e-2 * float(want.abs().max()), msg=f"{cls}.{name}")
 
 
 # ------------------------------------------------------------------ FFN

@@ -63,8 +63,8 @@ def test_attention_module_under_graph_replay(ir_text, flagkw):
     ref = orc.attention_block(f16(inp["X"]), f16(inp["WQ"]), f16(inp["WK"]), f16(inp["WV"]), f16(inp["K_cache"]), f16(inp["V_cache"]),
                               past=P, head_dim=D, noise=None if noise is None else f16(noise), **kw)
     # after 111 identical calls the result is still the single-call result (outputs are overwritten, not accumulated)
-    close(t["O2"], ref["O2"], rtol=1e-2, atol=2e-3, msg="O2 after graph replays")
-    close(t["K_cache"][:, P:], ref["K_new"], rtol=1e-2, atol=2e-3, msg="appended K rows")
+    close(t["O2"], ref["O2"], rtol=2e-2, atol=2e-2 * float(ref["O2"].abs().max()), msg="O2 after graph replays")
+    close(t["K_cache"][:, P:], ref["K_new"], rtol=2e-2, atol=2e-2 * float(ref["K_new"].abs().max()), msg="appended K rows")
     print(f"\n{m['KIND']}: {ms * 1e3:.1f} us per replay")
 
 

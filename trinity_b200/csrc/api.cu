@@ -172,9 +172,11 @@ struct AttnWs {
   float* lse2t;
   float* sum_a;  // fp32 staging of c_out / c_out1 when the caller's tensors are 16-bit
   float* sum_b;
+  float* partial;  // fp32 K-slice sums of the QKV projection (decode sizes only)
+  int split_qkv;
   size_t bytes;
 };
-static AttnWs carve_attn(const tb200_attn_args* a, void* base) {
+static AttnWs carve_attn(const tb200_attn_args* a, void* base, int num_sms) {
   Carver c(base);
   AttnWs w;
   const size_t T = static_cast<size_t>(a->batch) * a->seq;
@@ -190,13 +192,21 @@ static AttnWs carve_attn(const tb200_attn_args* a, void* base) {
   const bool stage = aux && a->aux_dtype != TB200_F32;
   w.sum_a = stage ? static_cast<float*>(c.take(keys * 4)) : nullptr;
   w.sum_b = (stage && (a->flags & TB200_ATTN_ROCO)) ? static_cast<float*>(c.take(keys * 4)) : nullptr;
+  // few tokens (decode): the projection streams the weights, so K is cut into slices until the SMs are filled
+  const int n_tiles = (a->n_q_heads * a->head_dim + kBN - 1) / kBN + 2 * ((a->n_kv_heads * a->head_dim + kBN - 1) / kBN);
+  w.split_qkv = choose_split(static_cast<int>(T), n_tiles, a->hidden, num_sms);
+  w.partial = w.split_qkv > 1
+                  ? static_cast<float*>(c.take(static_cast<size_t>(w.split_qkv) * T * (a->n_q_heads + 2 * a->n_kv_heads) * a->head_dim * 4))
+                  : nullptr;
   w.bytes = c.used;
   return w;
 }
 
 size_t tb200_attn_workspace_bytes(const tb200_attn_args* a) {
-  if (check_attn(a) != TB200_OK) return 0;
-  return carve_attn(a, nullptr).bytes;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st || check_attn(a) != TB200_OK) return 0;
+  return carve_attn(a, nullptr, st->num_sms).bytes;
 }
 
 // ev: null, or 5 events recorded on the stream at the stage boundaries
@@ -207,7 +217,7 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
   if ((status = check_attn(a)) != TB200_OK) return status;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->workspace == nullptr || !aligned16(a->workspace)) return TB200_ERR_WORKSPACE;
-  const AttnWs w = carve_attn(a, a->workspace);
+  const AttnWs w = carve_attn(a, a->workspace, st->num_sms);
   if (a->workspace_bytes < w.bytes) return TB200_ERR_WORKSPACE;
   const int T = a->batch * a->seq;
   const int D = a->head_dim;
@@ -245,7 +255,27 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
     g.qk_eps = a->qk_eps;
     g.q_norm_weight = a->q_norm_weight;
     g.k_norm_weight = a->k_norm_weight;
-    if ((status = launch_gemm(g, stream)) != TB200_OK) return status;
+    if (w.split_qkv > 1) {  // K slices into fp32 partial sums, then one small kernel with the same epilogue
+      g.mode = GEMM_PARTIAL;
+      g.row_scale = nullptr;
+      g.split_k = w.split_qkv;
+      g.partial = w.partial;
+      if ((status = launch_gemm(g, stream)) != TB200_OK) return status;
+      const int k_blocks = (a->hidden + kBK - 1) / kBK, per = (k_blocks + w.split_qkv - 1) / w.split_qkv;
+      QkvFinish f;
+      f.dtype = a->dtype;
+      f.M = T;
+      f.split_k = (k_blocks + per - 1) / per;
+      f.partial = w.partial;
+      f.row_scale = row_scale;
+      f.q_out = w.q; f.k_cache = a->k_cache; f.v_cache = a->v_cache;
+      f.S = a->seq; f.Hq = a->n_q_heads; f.Hkv = a->n_kv_heads; f.D = D; f.past = a->past; f.cache_len = a->cache_len;
+      f.qknorm = g.qknorm; f.qk_eps = a->qk_eps;
+      f.q_norm_weight = a->q_norm_weight; f.k_norm_weight = a->k_norm_weight;
+      if ((status = launch_qkv_finish(f, stream)) != TB200_OK) return status;
+    } else if ((status = launch_gemm(g, stream)) != TB200_OK) {
+      return status;
+    }
   }
   // 3. softmax(QK^T)V
   if (ev) cudaEventRecord(ev[2], stream);

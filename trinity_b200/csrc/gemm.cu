@@ -415,6 +415,56 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
   }
 }
 
+
+// ------------------------------------------------------------------ split-K finish of a QKV projection
+// One warp per (token row, head of q | k | v): the lanes cover the head's D columns, sum the K slices in a fixed
+// order, apply the row scale and the optional per-head RMSNorm (warp reduction), and write to q / the caches.
+template <typename T, int D>
+__global__ void qkv_finish_kernel(QkvFinish f) {
+  constexpr int V = D / 32;  // columns per lane
+  const int heads = f.Hq + 2 * f.Hkv;
+  const long long ldp = static_cast<long long>(heads) * D;
+  const int lane = threadIdx.x & 31;
+  const long long items = static_cast<long long>(f.M) * heads;
+  for (long long it = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; it < items;
+       it += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const int row = static_cast<int>(it / heads);
+    const int slot = static_cast<int>(it - static_cast<long long>(row) * heads);
+    float v[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = 0.f;
+    const float* src = f.partial + row * ldp + static_cast<long long>(slot) * D + lane * V;
+    for (int s = 0; s < f.split_k; ++s) {
+      const float* ps = src + static_cast<long long>(s) * f.M * ldp;
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] += ps[i];
+    }
+    const float rs = f.row_scale ? f.row_scale[row] : 1.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] *= rs;
+    const int which = slot < f.Hq ? 0 : (slot < f.Hq + f.Hkv ? 1 : 2);
+    const int head = which == 0 ? slot : (which == 1 ? slot - f.Hq : slot - f.Hq - f.Hkv);
+    if (f.qknorm && which < 2) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < V; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = rsqrtf(ss / static_cast<float>(D) + f.qk_eps);
+      const T* w = static_cast<const T*>(which == 0 ? f.q_norm_weight : f.k_norm_weight);
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] *= r * (w ? static_cast<float>(w[lane * V + i]) : 1.f);
+    }
+    const int b = row / f.S, s_in = row - b * f.S;
+    T* dst;
+    if (which == 0) dst = static_cast<T*>(f.q_out) + ((static_cast<long long>(b) * f.Hq + head) * f.S + s_in) * D;
+    else dst = static_cast<T*>(which == 1 ? f.k_cache : f.v_cache) + ((static_cast<long long>(b) * f.Hkv + head) * f.cache_len + f.past + s_in) * D;
+    uint32_t* d32 = reinterpret_cast<uint32_t*>(dst + lane * V);
+#pragma unroll
+    for (int i = 0; i < V; i += 2) d32[i >> 1] = Pack2<T>::pack(v[i], v[i + 1]);
+  }
+}
+
 template <typename T, int MODE>
 int launch_mode(const GemmParams& p, int grid, cudaStream_t stream) {
   static bool attr_set[32] = {};
@@ -540,6 +590,25 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
     splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
   } else if (f.dtype == TB200_F16) {
     splitk_finish_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
+  } else {
+    return TB200_ERR_UNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
+
+int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream) {
+  if (f.M <= 0 || f.split_k < 1 || !f.partial || !f.q_out || !f.k_cache || !f.v_cache || (f.D != 64 && f.D != 128) || f.S <= 0)
+    return TB200_ERR_INVALID;
+  const long long items = static_cast<long long>(f.M) * (f.Hq + 2 * f.Hkv);
+  long long blocks = (items * 32 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const unsigned g = static_cast<unsigned>(blocks);
+  if (f.dtype == TB200_BF16) {
+    if (f.D == 128) qkv_finish_kernel<__nv_bfloat16, 128><<<g, 256, 0, stream>>>(f);
+    else qkv_finish_kernel<__nv_bfloat16, 64><<<g, 256, 0, stream>>>(f);
+  } else if (f.dtype == TB200_F16) {
+    if (f.D == 128) qkv_finish_kernel<__half, 128><<<g, 256, 0, stream>>>(f);
+    else qkv_finish_kernel<__half, 64><<<g, 256, 0, stream>>>(f);
   } else {
     return TB200_ERR_UNSUPPORTED;
   }

@@ -93,6 +93,24 @@ struct SplitKFinish {
 };
 int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream);
 
+// Sum the K slices of a QKV projection and apply its epilogue (row scale, head split, optional per-head RMSNorm,
+// q head-major, k and v appended to the caches): the decode-size counterpart of GEMM_QKV.
+struct QkvFinish {
+  int dtype = TB200_BF16;
+  int M = 0, split_k = 1;
+  const float* partial = nullptr;   // (split_k, M, (Hq + 2 Hkv) * D)
+  const float* row_scale = nullptr;
+  void* q_out = nullptr;
+  void* k_cache = nullptr;
+  void* v_cache = nullptr;
+  int S = 0, Hq = 0, Hkv = 0, D = 0, past = 0, cache_len = 0;
+  int qknorm = 0;
+  float qk_eps = 0.f;
+  const void* q_norm_weight = nullptr;
+  const void* k_norm_weight = nullptr;
+};
+int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream);
+
 // ---------------------------------------------------------------- attn.cu
 struct AttnLaunch {
   int dtype = TB200_BF16;
