@@ -47,6 +47,9 @@ WORKLOADS = {
     "falcon_7b_gelu_ffn_m32768": dict(kind="ffn", M=32768, N=4544, P=18176, act="gelu", dtype="bf16"),
 }
 DEFAULT = "llama3_8b_vanilla_prefill_b8_s2048"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from an ncu capture of this very
+# command at full size (profiles/traffic_llama_b8_s2048.md); null where no capture has been taken.
+NCU_TRAFFIC = {"llama3_8b_vanilla_prefill_b8_s2048": 667_890_176}
 
 
 def block_flops(w, batch=None):
@@ -539,7 +542,8 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "gemm_kernel<bf16, QKV> (tcgen05 QKV projection)",
                          "achieved": gemm_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": (gemm_tflops / peak) if gemm_tflops else None, "peak_source": peaks["source"] + " burst cuBLAS bf16",
-                         "traffic": None, "flops_per_launch": proj / share, "ms_per_launch": stage[1]},
+                         "traffic": NCU_TRAFFIC.get(args.workload) if world == 1 else None, "flops_per_launch": proj / share,
+                         "ms_per_launch": stage[1]},
             "stages": {"rmsnorm_ms": stage[0], "qkv_gemm_ms": stage[1], "attention_ms": stage[2], "scores_ms": stage[3],
                        "qkv_gemm_tflops": gemm_tflops, "attention_tflops": attn_tflops,
                        "attention_frac_of_peak": (attn_tflops / peak) if attn_tflops else None},
