@@ -1,0 +1,63 @@
+"""Record what the reference's code generator declares for a sample of its own IR candidates.
+
+    python tests/golden/make_ir_fixtures.py --ref /path/to/Trinity
+
+For a few candidates of every block family (the best recorded one plus a spread over the sweep) it runs the reference's
+``convert_ir_to_triton`` (``codegen/convert_module.py:5-13``; pure Python, no GPU) on the IR text stored in
+``evaluation/**/*.json`` and keeps the IR together with the ``TENSOR_PARAMS`` / ``BLOCK_PARAMS`` lines of the module it
+emits.  ``tests/test_codegen.py`` checks the replacement generator against these.
+"""
+import argparse
+import json
+import os
+import re
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+FAMILIES = {
+    "vanilla": ("evaluation/vanilla/vanilla_llama.json", 28142),
+    "prenorm": ("evaluation/prenorm/prenorm_llama.json", 579),
+    "qknorm": ("evaluation/qknorm/qknorm_llama.json", 54735),
+    "keyformer": ("evaluation/keyformer/keyformer_llama.json", 1813),
+    "roco": ("evaluation/roco/roco_llama.json", 1753),
+    "ffn_llama": ("evaluation/ffn/ffn_llama/benchmark_ffn_llama.json", 2248),
+    "ffn_falcon": ("evaluation/ffn/ffn_falcon/benchmark_ffn_final.json", 428),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--per-family", type=int, default=4)
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(args.ref, "codegen"))
+    from convert_module import convert_ir_to_triton  # the reference's
+
+    out = []
+    for family, (rel, best) in FAMILIES.items():
+        rows = json.load(open(os.path.join(args.ref, rel)))
+        rows = [r for r in rows if r.get("ir_expression") and not r.get("error")]
+        picked = [r for r in rows if r["ir_id"] == best][:1]
+        step = max(1, len(rows) // args.per_family)
+        picked += [r for r in rows[::step] if r["ir_id"] != best][: args.per_family - len(picked)]
+        for r in picked:
+            shapes = None
+            try:
+                text = convert_ir_to_triton(r["ir_expression"], shapes, r["tensor_config"])
+            except Exception as e:  # the reference generator needs the shape table for some candidates
+                print("skip", family, r["ir_id"], type(e).__name__)
+                continue
+            tp = re.search(r"^TENSOR_PARAMS = (\[.*\])$", text, re.M)
+            bp = re.search(r"^BLOCK_PARAMS = (\[.*\])$", text, re.M)
+            if not tp or not bp:
+                continue
+            out.append({"family": family, "ir_id": r["ir_id"], "constants": r["tensor_config"], "ir": r["ir_expression"],
+                        "tensor_params": json.loads(tp.group(1).replace("'", '"')),
+                        "block_params": json.loads(bp.group(1).replace("'", '"'))})
+    json.dump(out, open(os.path.join(HERE, "ir_modules.json"), "w"), indent=0)
+    print("wrote", len(out), "fixtures")
+
+
+if __name__ == "__main__":
+    main()

@@ -70,3 +70,21 @@ def test_errors_are_exceptions():
         convert_ir_to_triton("(seq (store (output O2)", None, {})
     with pytest.raises(ValueError):
         convert_ir_to_triton("", None, {})
+
+
+def test_parameter_lists_match_the_reference_generator(golden_dir):
+    """IR candidates from the reference's own sweeps (evaluation/**/*.json) with the TENSOR_PARAMS / BLOCK_PARAMS its
+    generator emitted for them (tests/golden/make_ir_fixtures.py): the replacement must declare the same lists, or the
+    harness's positional call forward(*tensors) would bind the wrong tensors."""
+    import json
+    import os
+    fixtures = json.load(open(os.path.join(golden_dir, "ir_modules.json")))
+    assert len(fixtures) >= 20
+    seen = set()
+    for f in fixtures:
+        m = load(convert_ir_to_triton(f["ir"], None, f["constants"]))
+        assert m["TENSOR_PARAMS"] == f["tensor_params"], (f["family"], f["ir_id"])
+        assert m["BLOCK_PARAMS"] == f["block_params"], (f["family"], f["ir_id"])
+        assert m["KIND"].split("_prenorm")[0] in (f["family"], f["family"].replace("prenorm", "vanilla")) or m["KIND"] == f["family"]
+        seen.add(f["family"])
+    assert seen == {"vanilla", "prenorm", "qknorm", "keyformer", "roco", "ffn_llama", "ffn_falcon"}

@@ -53,6 +53,8 @@ def parse(ir_code: str) -> Node:
 class KernelUse:
     stores: Set[str] = field(default_factory=set)
     loads: Set[str] = field(default_factory=set)
+    store_index: dict = field(default_factory=dict)   # name -> set of index expressions it is stored with
+    load_index: dict = field(default_factory=dict)    # name -> set of index expressions it is loaded with
 
 
 @dataclass
@@ -64,14 +66,20 @@ class IrSummary:
     kernels: List[KernelUse] = field(default_factory=list)
 
     def cross_kernel(self) -> Set[str]:
-        """Intermediates written by one kernel and read by another: they live in HBM and are module
-        parameters (``codegen/TritonGen.py:1018-1053``)."""
+        """Intermediates that live in HBM and are therefore module parameters: written by one kernel and read by
+        another (``codegen/TritonGen.py:1018-1053``), or written and re-read inside one kernel through a different
+        index expression (another tiling of the same tensor cannot stay in registers)."""
         out: Set[str] = set()
         for name in self.tensors:
             writers = {i for i, k in enumerate(self.kernels) if name in k.stores}
             readers = {i for i, k in enumerate(self.kernels) if name in k.loads}
             if writers and readers and (readers - writers or len(writers) > 1):
                 out.add(name)
+                continue
+            for k in self.kernels:
+                st, ld = k.store_index.get(name, set()), k.load_index.get(name, set())
+                if st and ld and (ld - st):
+                    out.add(name)
         return out
 
 
@@ -115,10 +123,16 @@ def summarize(ir_code: str) -> IrSummary:
         elif head == "store":
             if len(n) != 4:
                 raise ValueError("malformed store")
-            use.stores.update(names(n[1]))
+            got = names(n[1])
+            use.stores.update(got)
+            for name in got:
+                use.store_index.setdefault(name, set()).add(repr(n[3]))
             walk(n[2], use)
         elif head == "load":
-            use.loads.update(names(n[1]))
+            got = names(n[1])
+            use.loads.update(got)
+            for name in got:
+                use.load_index.setdefault(name, set()).add(repr(n[2]) if len(n) > 2 else "")
         else:
             for child in n[1:]:
                 walk(child, use)
