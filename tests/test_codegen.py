@@ -15,7 +15,7 @@ VANILLA = ATTN % ""
 PRENORM = VANILLA.replace("(seq (sloop 0 4096 tile_k k (store", "(seq (sloop 0 4096 tile_k k (seq (store (tensor X2) (rsum (sqr (load (input X) (index fulltile (tile k)))) 1) (index fulltile)) (store", 1).replace("(index fulltile (tile n)))) (seq (store (input K_cache", "(index fulltile (tile n))))) (seq (store (input K_cache", 1)
 KEYFORMER = ATTN % "(seq (store (output C_out) (load (input noise) (index (elem n) fulltile fulltile)) (index (elem n) fulltile)) "
 KEYFORMER = KEYFORMER[:-1] + "))"
-ROCO = ATTN % "(seq (store (output C_out1) (load (tensor C_exp) (index (elem n) fulltile fulltile)) (index (elem n) fulltile)) (seq (store (output C_out2) (load (tensor C_exp) (index (elem n) fulltile fulltile)) (index (elem n) fulltile)) "
+ROCO = ATTN % "(seq (store (output C_out1) (load (tensor C_exp) (index (elem n) fulltile (tile p))) (index (elem n) fulltile)) (seq (store (output C_out2) (load (tensor C_exp) (index (elem n) fulltile (tile p))) (index (elem n) fulltile)) "
 ROCO = ROCO[:-1] + ")))"
 TWO_KERNELS = ("(seq (ploop 0 4096 128 n (store (tensor O) (* (load (input X) (index fulltile)) (load (input WQ,WK,WV) (index fulltile (tile n)))) (index (elem n) fulltile fulltile))) "
                "(ploop 0 4096 128 n (store (output O2) (load (tensor O) (index (elem n) fulltile fulltile)) (index fulltile (tile n)))))")
