@@ -420,8 +420,6 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   if (!(a.sm_scale > 0.f)) return TB200_ERR_INVALID;  // the row maximum is taken before scaling
   if (a.noise == nullptr) {
     static const bool single_tile = getenv("TB200_ATTN_SINGLE_TILE") != nullptr;  // A/B switch for measurements
-    static const bool decoupled = getenv("TB200_ATTN_DECOUPLED") != nullptr;
-    if (decoupled) return launch_attn_fwd_decoupled(a, stream);
     if (!single_tile) return launch_attn_fwd_pingpong(a, stream);
   }
 

@@ -130,8 +130,6 @@ struct AttnLaunch {
 int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream);
 // attn2.cu: two query tiles per CTA; chosen by launch_attn_fwd when there is no noise tensor
 int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream);
-// attn3.cu: two query tiles per CTA, P through shared memory so that S_{j+1} is computed during softmax(j)
-int launch_attn_fwd_decoupled(const AttnLaunch& a, cudaStream_t stream);
 
 // ---------------------------------------------------------------- score.cu
 struct ScoreLaunch {
