@@ -174,6 +174,9 @@ struct AttnWs {
   float* sum_b;
   float* partial;  // fp32 K-slice sums of the QKV projection (decode sizes only)
   int split_qkv;
+  int kv_splits;   // attention over a split key range (decode sizes only)
+  float* part_o;
+  float* part_ml;
   size_t bytes;
 };
 static AttnWs carve_attn(const tb200_attn_args* a, void* base, int num_sms) {
@@ -198,6 +201,9 @@ static AttnWs carve_attn(const tb200_attn_args* a, void* base, int num_sms) {
   w.partial = w.split_qkv > 1
                   ? static_cast<float*>(c.take(static_cast<size_t>(w.split_qkv) * T * (a->n_q_heads + 2 * a->n_kv_heads) * a->head_dim * 4))
                   : nullptr;
+  w.kv_splits = (a->flags & TB200_ATTN_KEYFORMER) ? 1 : attn_kv_splits(a->batch, a->seq, a->n_q_heads, a->past + a->seq, num_sms);
+  w.part_o = w.kv_splits > 1 ? static_cast<float*>(c.take(static_cast<size_t>(w.kv_splits) * rows * a->head_dim * 4)) : nullptr;
+  w.part_ml = w.kv_splits > 1 ? static_cast<float*>(c.take(static_cast<size_t>(w.kv_splits) * rows * 2 * 4)) : nullptr;
   w.bytes = c.used;
   return w;
 }
@@ -287,6 +293,7 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
     f.sm_scale = a->sm_scale;
     f.q = w.q; f.k_cache = a->k_cache; f.v_cache = a->v_cache; f.o2 = a->o2;
     f.lse2 = w.lse2;
+    f.kv_splits = w.kv_splits; f.part_o = w.part_o; f.part_ml = w.part_ml;
     if (a->flags & TB200_ATTN_KEYFORMER) {
       f.noise = a->noise;
       f.tau = a->tau;

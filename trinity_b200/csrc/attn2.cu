@@ -48,6 +48,9 @@ struct Attn2Params {
   float scale_log2;
   void* o2;
   float* lse2;
+  int kv_splits;     // > 1: the key tiles are dealt out over this many CTAs, which leave partial results
+  float* part_o;     // (kv_splits, B, Hq, S, D) fp32, unnormalised
+  float* part_ml;    // (kv_splits, B, Hq, S, 2): exponent reference and row sum of each part
   int* err;
   long long* trace;  // timing probes (TB200_TRACE builds only)
 };
@@ -79,7 +82,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_blocks = (p.S + 2 * BQ - 1) / (2 * BQ);
-  const int q0 = (n_blocks - 1 - blockIdx.x) * 2 * BQ;  // longest blocks first
+  const int blk = blockIdx.x / p.kv_splits;
+  const int sp = blockIdx.x - blk * p.kv_splits;         // which share of the key tiles this CTA takes
+  const int q0 = (n_blocks - 1 - blk) * 2 * BQ;          // longest blocks first
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
   const int hkv = hq / (p.Hq / p.Hkv);
@@ -91,6 +96,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
     nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
   }
+  // key tiles [j_begin, j_begin + nt[t]) of each query tile; local index j below, global j_begin + j for coordinates
+  const int per_split = (max(nt[0], nt[1]) + p.kv_splits - 1) / p.kv_splits;
+  const int j_begin = sp * per_split;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) nt[t] = max(0, min(nt[t], j_begin + per_split) - j_begin);
   const int nt_max = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
@@ -125,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && nt_max > 0) {
       mbar_arrive_expect_tx(q_full, 2 * L::kTile);
 #pragma unroll
       for (int t = 0; t < 2; ++t)
@@ -142,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         mbar_arrive_expect_tx(&k_full[st], L::kTile);
 #pragma unroll
         for (int dc = 0; dc < D / 64; ++dc)
-          tma_load_3d(smem + L::kKOff + st * L::kTile + dc * (BKV * 128), &p.map_k, &k_full[st], dc * 64, j * BKV, b * p.Hkv + hkv);
+          tma_load_3d(smem + L::kKOff + st * L::kTile + dc * (BKV * 128), &p.map_k, &k_full[st], dc * 64, (j_begin + j) * BKV, b * p.Hkv + hkv);
       }
       __syncwarp();
       if (!mbar_wait(&v_empty[st], ph ^ 1, ctx, 402)) break;
@@ -150,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         mbar_arrive_expect_tx(&v_full[st], L::kTile);
 #pragma unroll
         for (int dc = 0; dc < D / 64; ++dc)
-          tma_load_3d(smem + L::kVOff + st * L::kTile + dc * (BKV * 128), &p.map_v, &v_full[st], dc * 64, j * BKV, b * p.Hkv + hkv);
+          tma_load_3d(smem + L::kVOff + st * L::kTile + dc * (BKV * 128), &p.map_v, &v_full[st], dc * 64, (j_begin + j) * BKV, b * p.Hkv + hkv);
       }
       __syncwarp();
     }
@@ -180,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
                      (j > 0 || kk > 0) ? 1u : 0u);
       umma_commit_warp(&pv_done[t]);
     };
-    bool ok = mbar_wait(q_full, 0, ctx, 403) && mbar_wait(&k_full[0], 0, ctx, 404);
+    bool ok = nt_max > 0 && mbar_wait(q_full, 0, ctx, 403) && mbar_wait(&k_full[0], 0, ctx, 404);
     if (ok) {
       tc_fence_after();
       if (nt[0] > 0) issue_s(0, 0);
@@ -237,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     bool ok = true;
 
     for (int j = 0; j < my_nt; ++j) {
-      const int k0 = j * BKV + h * CW;
+      const int k0 = (j_begin + j) * BKV + h * CW;
       TRACE((t * 32 + j) * 8 + 0, r_in == 0 && h == 0 && j < 32);
       if (!mbar_wait(&s_full[t], j & 1, ctx, 408)) { ok = false; break; }
       tc_fence_after();
@@ -324,7 +334,33 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       ok = mbar_wait(&row_xch[t], my_nt & 1, ctx, 411);
       if (ok) l += xsum[(h ^ 1) * 128 + r_in];
     }
-    if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
+    if (p.kv_splits > 1) {
+      // this CTA saw only a share of the keys: leave the unnormalised accumulator, its exponent reference and its row
+      // sum; attn_combine_kernel merges the shares.  A share without keys leaves the neutral element.
+      const long long prow = ((static_cast<long long>(sp) * p.B + b) * p.Hq + hq) * p.S + qi;
+      const bool have = ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409);
+      if (have) tc_fence_after();
+      uint32_t o[32];
+#pragma unroll 1
+      for (int c = 0; c < OW / 32; ++c) {
+        if (have) {  // uniform over the warp
+          tmem_ld_x32(tmem_o + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row_ok) {
+          uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D + h * OW + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+      }
+      if (row_ok && h == 0) {
+        p.part_ml[prow * 2] = have ? m_use : -INFINITY;
+        p.part_ml[prow * 2 + 1] = have ? l : 0.f;
+      }
+    } else if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
       tc_fence_after();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
       T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(b) * p.S + qi) * p.Hq + hq) * D + h * OW;
@@ -355,6 +391,39 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   }
 }
 
+// Merge the shares of a key-split launch: one warp per (batch, head, query) row, lanes over the D columns.
+template <typename T, int D>
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ o2,
+                                    float* __restrict__ lse2, int splits, int B, int Hq, int S) {
+  constexpr int V = D / 32;
+  const long long rows = static_cast<long long>(B) * Hq * S;
+  const int lane = threadIdx.x & 31;
+  for (long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows;
+       row += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(s * rows + row) * 2]);
+    float l = 0.f, acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {  // fixed order: deterministic
+      const float ms = part_ml[(s * rows + row) * 2];
+      const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);
+      l = fmaf(w, part_ml[(s * rows + row) * 2 + 1], l);
+      const float* po = part_o + (s * rows + row) * D + lane * V;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fmaf(w, po[i], acc[i]);
+    }
+    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    const int qi = static_cast<int>(row % S);
+    const int hq = static_cast<int>((row / S) % Hq);
+    const int b = static_cast<int>(row / (static_cast<long long>(S) * Hq));
+    uint32_t* dst = reinterpret_cast<uint32_t*>(o2 + ((static_cast<long long>(b) * S + qi) * Hq + hq) * D + lane * V);
+#pragma unroll
+    for (int i = 0; i < V; i += 2) dst[i >> 1] = Pack2<T>::pack(acc[i] * inv_l, acc[i + 1] * inv_l);
+    if (lane == 0 && lse2 != nullptr) lse2[row] = m + log2f(l);
+  }
+}
+
 template <typename T, int D>
 int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
   static bool attr_set[32] = {};
@@ -366,10 +435,31 @@ int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
     attr_set[dev & 31] = true;
   }
   attn_fwd2_kernel<T, D><<<grid, kThreads, Smem2<D>::kTotal, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
+  if (p.kv_splits > 1) {
+    const long long rows = static_cast<long long>(p.B) * p.Hq * p.S;
+    long long blocks = (rows * 32 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    attn_combine_kernel<T, D><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.part_o, p.part_ml, static_cast<T*>(p.o2), p.lse2,
+                                                                             p.kv_splits, p.B, p.Hq, p.S);
+    if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
+  }
+  return TB200_OK;
 }
 
 }  // namespace
+
+// With few (query block, head, batch) CTAs and many key tiles -- the decode shapes -- the key range is dealt out over
+// several CTAs per block so that the SMs are filled; 1 = no split.
+int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms) {
+  const long long ctas = static_cast<long long>((S + 2 * BQ - 1) / (2 * BQ)) * Hq * B;
+  const int tiles = (kv_len + BKV - 1) / BKV;
+  if (ctas * 2 > num_sms || tiles < 4) return 1;
+  int s = static_cast<int>(num_sms / ctas);
+  if (s > tiles / 2) s = tiles / 2;
+  if (s > 16) s = 16;
+  return s < 2 ? 1 : s;
+}
 
 // Same contract as launch_attn_fwd without the KeyFormer statistic; arguments are validated by the caller.
 int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
@@ -382,6 +472,9 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * kLog2e;
   p.o2 = a.o2;
   p.lse2 = a.lse2;
+  p.kv_splits = (a.kv_splits > 1 && a.part_o != nullptr && a.part_ml != nullptr) ? a.kv_splits : 1;
+  p.part_o = a.part_o;
+  p.part_ml = a.part_ml;
   p.err = st->err_word;
 #ifdef TB200_TRACE
   if (const char* tp = getenv("TB200_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(tp, nullptr, 0));
@@ -400,7 +493,7 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
     if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
   }
-  const dim3 grid((a.S + 2 * BQ - 1) / (2 * BQ), a.Hq, a.B);
+  const dim3 grid(((a.S + 2 * BQ - 1) / (2 * BQ)) * p.kv_splits, a.Hq, a.B);
   if (a.dtype == TB200_BF16) {
     return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
   }

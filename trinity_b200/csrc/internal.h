@@ -126,10 +126,15 @@ struct AttnLaunch {
   const void* noise = nullptr;      // (B,Hq,S,past+S)
   float tau = 1.f;
   float* lse2_perturbed = nullptr;  // (B,Hq,S)
+  // decode shapes: key range split over CTAs (attn_kv_splits); partial results in caller-provided workspace
+  int kv_splits = 1;
+  float* part_o = nullptr;          // (kv_splits,B,Hq,S,D) fp32
+  float* part_ml = nullptr;         // (kv_splits,B,Hq,S,2) fp32
 };
 int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream);
 // attn2.cu: two query tiles per CTA; chosen by launch_attn_fwd when there is no noise tensor
 int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream);
+int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms);
 
 // ---------------------------------------------------------------- score.cu
 struct ScoreLaunch {
