@@ -35,7 +35,7 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + slack to align the ring to 1 KiB
 constexpr int kThreads = 192;
-constexpr int kGroupM = 16;
+constexpr int kGroupM = 32;
 constexpr int kTmemCols = 512;
 
 struct GemmParams {
