@@ -15,6 +15,7 @@
 //   GEMM_QKV                   tiles walk Wq, then Wk, then Wv; the epilogue splits heads, optionally
 //                              RMS-normalises each head of q and k, writes q head-major and appends k, v
 //                              to the caches
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -37,6 +38,11 @@ constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + s
 constexpr int kThreads = 192;
 constexpr int kGroupM = 32;
 constexpr int kTmemCols = 512;
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 256 tile.  Each CTA stages its own 128 A
+// rows and HALF of the B columns (two boxes), so a stage is 32 KiB and six stages fit where four did.
+constexpr int kStagesPair = 6;
+constexpr int kStageBytesPair = kABytes + 2 * kBChunkBytes;
+static_assert(kStagesPair * kStageBytesPair == kStages * kStageBytes, "both variants use the same shared-memory size");
 
 struct GemmParams {
   CUtensorMap map_a;
@@ -71,7 +77,15 @@ struct Unit {
   int m0, src, n0, kb_begin, kb_end, split;
 };
 
-__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
+template <bool PAIR>
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, int code) {
+  if (PAIR) return mbar_wait_cluster(bar, parity, ctx, code);
+  return mbar_wait(bar, parity, ctx, code);
+}
+
+// rank: position of this CTA in its pair (0 when CTAs work alone); a pair's tile is 2 * BM rows tall.
+template <bool PAIR>
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u, int rank) {
   Unit r;
   const int tile = u / p.split_k;
   r.split = u - tile * p.split_k;
@@ -82,7 +96,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
   const int rows_here = min(kGroupM, p.m_tiles - g * kGroupM);
   const int nt = rem / rows_here;
   const int mt = g * kGroupM + (rem - nt * rows_here);
-  r.m0 = mt * BM;
+  r.m0 = PAIR ? (mt * 2 + rank) * BM : mt * BM;
   int src = 0;
   while (src + 1 < p.n_src && nt >= p.src_tile0[src + 1]) ++src;
   if (p.tile_n != BN) src = 0;  // SwiGLU: both sources are walked together
@@ -117,41 +131,52 @@ __device__ __forceinline__ void store32_clipped(T* dst, const float (&v)[32], in
   }
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int NST = PAIR ? kStagesPair : kStages;
+  constexpr int NCH = PAIR ? 2 : 4;  // B boxes this CTA stages
+  constexpr int SB = kABytes + NCH * kBChunkBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* empty = full + kStages;
-  uint64_t* tfull = empty + kStages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * SB);
+  uint64_t* empty = full + NST;
+  uint64_t* tfull = empty + NST;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int unit0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int unit_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tempty[a], PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs of a pair, on the leader)
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {  // the same warp of both CTAs of the pair allocates together
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&p.map_a);
     for (int s = 0; s < p.n_src; ++s) tma_prefetch_desc(&p.map_b[s]);
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();  // a pair's barriers must exist before its peer signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const AbortCtx ctx{p.err, abort_flag};
@@ -161,64 +186,85 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x) {
-      const Unit t = decode_unit(p, u);
+    for (int u = unit0; ok && u < p.total_units; u += unit_step) {
+      const Unit t = decode_unit<PAIR>(p, u, rank);
       for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
-        if (!mbar_wait(&empty[stage], phase ^ 1, ctx, 101)) { ok = false; break; }
+        if (!wait_bar<PAIR>(&empty[stage], phase ^ 1, ctx, 101)) { ok = false; break; }
         if (lane == 0) {
-          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sa = smem + stage * SB;
           uint8_t* sb = sa + kABytes;
-          mbar_arrive_expect_tx(&full[stage], kStageBytes);
-          tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
+          if (PAIR) {
+            // both CTAs' boxes are counted on the leader's barrier; the leader announces the pair's bytes
+            const uint32_t fb = mapa_u32(smem_u32(&full[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * SB);
+            tma_load_2d_pair(sa, &p.map_a, fb, kb * BK, t.m0);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            int src = t.src, col = t.n0 + 64 * c;
-            if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
-            tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
+            for (int c = 0; c < NCH; ++c) {
+              const int g = rank * NCH + c;  // box of the pair's 256-column B tile
+              int src = t.src, col = t.n0 + 64 * g;
+              if (MODE == GEMM_SWIGLU) { src = g >> 1; col = t.n0 + 64 * (g & 1); }
+              tma_load_2d_pair(sb + c * kBChunkBytes, &p.map_b[src], fb, col, kb * BK);
+            }
+          } else {
+            mbar_arrive_expect_tx(&full[stage], SB);
+            tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              int src = t.src, col = t.n0 + 64 * c;
+              if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
+              tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
+            }
           }
         }
         __syncwarp();
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++stage == NST) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, BM, BN);
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------------------------ MMA issuer (a pair's leader issues for both CTAs)
+    constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, PAIR ? 2 * BM : BM, BN);
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x) {
-      const Unit t = decode_unit(p, u);
-      if (!mbar_wait(&tempty[acc], acc_phase ^ 1, ctx, 102)) break;
+    for (int u = unit0; ok && u < p.total_units; u += unit_step) {
+      const Unit t = decode_unit<PAIR>(p, u, rank);
+      if (!wait_bar<PAIR>(&tempty[acc], acc_phase ^ 1, ctx, 102)) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
-        if (!mbar_wait(&full[stage], phase, ctx, 103)) { ok = false; break; }
+        if (!wait_bar<PAIR>(&full[stage], phase, ctx, 103)) { ok = false; break; }
         tc_fence_after();
         {  // all lanes converged, operands warp-uniform, one elected lane issues
-          const uint32_t a0 = smem_u32(smem + stage * kStageBytes);
+          const uint32_t a0 = smem_u32(smem + stage * SB);
           const uint64_t ad = make_smem_desc(a0, 16, 1024);
           const uint64_t bd = make_smem_desc(a0 + kABytes, kBChunkBytes, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // K-major A: +32 B per 16 K; MN-major B: +16 K-rows (2048 B); in 16-byte units
-            umma_ss_warp(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 128), idesc,
-                         (kb > t.kb_begin || k > 0) ? 1u : 0u);
-          umma_commit_warp(&empty[stage]);                       // frees the stage when these MMAs have read it
-          if (kb == t.kb_end - 1) umma_commit_warp(&tfull[acc]);  // accumulator complete
+          for (int k = 0; k < BK / 16; ++k) {  // K-major A: +32 B per 16 K; MN-major B: +16 K-rows (2048 B); in 16-byte units
+            const uint32_t accum = (kb > t.kb_begin || k > 0) ? 1u : 0u;
+            if (PAIR) umma_ss_pair_warp(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 128), idesc, accum);
+            else umma_ss_warp(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 128), idesc, accum);
+          }
+          if (PAIR) {  // the arrivals land on the same barrier of both CTAs
+            umma_commit_pair_warp(&empty[stage]);
+            if (kb == t.kb_end - 1) umma_commit_pair_warp(&tfull[acc]);
+          } else {
+            umma_commit_warp(&empty[stage]);                       // frees the stage when these MMAs have read it
+            if (kb == t.kb_end - 1) umma_commit_warp(&tfull[acc]);  // accumulator complete
+          }
         }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++stage == NST) { stage = 0; phase ^= 1; }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
-      const Unit t = decode_unit(p, u);
-      if (!mbar_wait(&tfull[acc], acc_phase, ctx, 104)) break;
+    for (int u = unit0; u < p.total_units; u += unit_step) {
+      const Unit t = decode_unit<PAIR>(p, u, rank);
+      if (!wait_bar<PAIR>(&tfull[acc], acc_phase, ctx, 104)) break;
       tc_fence_after();
       const int row = t.m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
@@ -355,17 +401,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+        else mbar_arrive(&tempty[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
   }
 
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();  // neither CTA of a pair leaves while its peer may still reach it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -465,29 +515,70 @@ __global__ void qkv_finish_kernel(QkvFinish f) {
   }
 }
 
-template <typename T, int MODE>
-int launch_mode(const GemmParams& p, int grid, cudaStream_t stream) {
+// PAIR: the grid is made of clusters of two CTAs; `slots` is the SM count for single CTAs and is replaced by the
+// number of pairs the device can hold at once (asked of the runtime once per device) for pairs.
+template <typename T, int MODE, bool PAIR>
+int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
   static bool attr_set[32] = {};
+  static int max_pairs[32] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  if (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(gemm_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_kernel<T, MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return TB200_ERR_CUDA;
+    if (PAIR) {
+      cfg.gridDim = dim3(static_cast<unsigned>(slots / 2 * 2), 1, 1);
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<T, MODE, PAIR>, &cfg) != cudaSuccess || n < 1) return TB200_ERR_CUDA;
+      max_pairs[dev & 31] = n < slots / 2 ? n : slots / 2;
+    }
     attr_set[dev & 31] = true;
   }
-  gemm_kernel<T, MODE><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  int ctas = slots;
+  if (PAIR) ctas = 2 * max_pairs[dev & 31];
+  if (PAIR) ctas = p.total_units * 2 < ctas ? p.total_units * 2 : ctas;
+  else ctas = p.total_units < ctas ? p.total_units : ctas;
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  if (cudaLaunchKernelEx(&cfg, gemm_kernel<T, MODE, PAIR>, p) != cudaSuccess) return TB200_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
-template <typename T>
-int launch_typed(const GemmParams& p, int mode, int grid, cudaStream_t stream) {
+template <typename T, bool PAIR>
+int launch_typed(const GemmParams& p, int mode, int slots, cudaStream_t stream) {
   switch (mode) {
-    case GEMM_STORE: return launch_mode<T, GEMM_STORE>(p, grid, stream);
-    case GEMM_SWIGLU: return launch_mode<T, GEMM_SWIGLU>(p, grid, stream);
-    case GEMM_QKV: return launch_mode<T, GEMM_QKV>(p, grid, stream);
-    case GEMM_PARTIAL: return launch_mode<T, GEMM_PARTIAL>(p, grid, stream);
+    case GEMM_STORE: return launch_mode<T, GEMM_STORE, PAIR>(p, slots, stream);
+    case GEMM_SWIGLU: return launch_mode<T, GEMM_SWIGLU, PAIR>(p, slots, stream);
+    case GEMM_QKV: return launch_mode<T, GEMM_QKV, PAIR>(p, slots, stream);
+    case GEMM_PARTIAL: return launch_mode<T, GEMM_PARTIAL, PAIR>(p, slots, stream);
     default: return TB200_ERR_UNSUPPORTED;
   }
+}
+
+// Pairs halve the B bytes each SM stages (measured +1.3 .. +4 % on 16384-row projections); they pay off when
+// there is a 256-row tile for every pair of SMs, so decode-size M keeps single CTAs.
+// TB200_GEMM_PAIR=0/1 forces the choice for every M >= 256 (read once).
+bool use_pair(int M, long long pair_units, int num_sms) {
+  static const int forced = [] {
+    const char* e = getenv("TB200_GEMM_PAIR");
+    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+  }();
+  if (M < 2 * BM) return false;
+  if (forced >= 0) return forced == 1;
+  return pair_units >= num_sms / 2;
 }
 
 }  // namespace
@@ -512,7 +603,6 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty slice
   p.n_src = g.n_src;
   p.tile_n = (g.mode == GEMM_SWIGLU) ? 128 : BN;
-  p.m_tiles = (g.M + BM - 1) / BM;
   int tiles = 0;
   for (int s = 0; s < g.n_src; ++s) {
     if (g.B[s] == nullptr || g.N[s] <= 0 || (g.N[s] & 7) != 0 || !aligned16(g.B[s])) return TB200_ERR_INVALID;
@@ -539,6 +629,8 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   for (int s = g.n_src; s < 4; ++s) p.src_tile0[s] = tiles;
   p.src_tile0[g.n_src] = tiles;
   p.n_tiles = tiles;
+  const bool pair = use_pair(g.M, static_cast<long long>((g.M + 2 * BM - 1) / (2 * BM)) * tiles * p.split_k, st->num_sms);
+  p.m_tiles = pair ? (g.M + 2 * BM - 1) / (2 * BM) : (g.M + BM - 1) / BM;
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.split_k;
   if (units > 0x7fffffffLL) return TB200_ERR_INVALID;
   p.total_units = static_cast<int>(units);
@@ -575,9 +667,12 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     const uint32_t box[2] = {64, BK};
     if ((status = make_tensor_map(&p.map_b[s], g.B[s], 2, dims, strides, box)) != TB200_OK) return status;
   }
-  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-  if (g.dtype == TB200_BF16) return launch_typed<__nv_bfloat16>(p, g.mode, grid, stream);
-  return launch_typed<__half>(p, g.mode, grid, stream);
+  if (pair) {
+    if (g.dtype == TB200_BF16) return launch_typed<__nv_bfloat16, true>(p, g.mode, st->num_sms, stream);
+    return launch_typed<__half, true>(p, g.mode, st->num_sms, stream);
+  }
+  if (g.dtype == TB200_BF16) return launch_typed<__nv_bfloat16, false>(p, g.mode, st->num_sms, stream);
+  return launch_typed<__half, false>(p, g.mode, st->num_sms, stream);
 }
 
 int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
@@ -725,9 +820,8 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
     const uint32_t box[2] = {64, BK};
     if ((status = make_tensor_map(&p.map_b[s], srcs[s], 2, dims, strides, box)) != TB200_OK) return status;
   }
-  const int grid = p.total_units < st->num_sms ? p.total_units : st->num_sms;
-  status = (a->dtype == TB200_BF16) ? launch_typed<__nv_bfloat16>(p, GEMM_PARTIAL, grid, stream)
-                                    : launch_typed<__half>(p, GEMM_PARTIAL, grid, stream);
+  status = (a->dtype == TB200_BF16) ? launch_typed<__nv_bfloat16, false>(p, GEMM_PARTIAL, st->num_sms, stream)
+                                    : launch_typed<__half, false>(p, GEMM_PARTIAL, st->num_sms, stream);
   if (status != TB200_OK) return status;
   SplitKFinish f;
   f.dtype = a->dtype;
