@@ -1,16 +1,26 @@
 // Attention forward, two query tiles per CTA ("ping-pong"): the kernel used when no noise tensor is involved.
 //
-// One CTA per (256 queries, q head, batch element), 320 threads (kHalves = 1):
-//   warp 0      TMA producer: both Q tiles once, then K and V tiles of 128 keys through two-deep rings
-//   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}
+// Persistent: one CTA per SM walks work items (256 queries, q head, batch element[, share of the keys]), longest
+// items first.  320 threads:
+//   warp 0      TMA producer: the two Q tiles of an item, then its K and V tiles of 128 keys through two-deep rings
+//               that run on across items
+//   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}; in the last step of
+//               an item the S_0 tiles of the NEXT item take the place of S_{j+1}
 //   warps 2-5   softmax of query tile 0          warps 6-9   softmax of query tile 1
 // While one softmax warpgroup works on its S tile the tensor core serves the other tile, and each SM sub-partition
 // holds two softmax warps whose MUFU / FMA / TMEM latencies overlap.  K and V tiles are fetched once for 256 queries.
+// Across items the pipeline does not drain: while a warpgroup normalises and stores O of item i, the Q tiles of item
+// i+1 are already in shared memory and its first S tile is in tensor memory.
 //
 // Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
 // P_j (16-bit) is written back over the first 64 columns of its own S tile and is the A operand of P_j V_j straight
 // from tensor memory (no shared-memory round trip).  MMAs issued by one thread complete in issue order, so S_{j+1}
 // (issued after P_j V_j) cannot overwrite P_j early, and an arrival on s_full also means the previous P V is done.
+// The first P V of an item overwrites O, so it waits until the warpgroup has read the previous item's O (o_free).
+//
+// One thread owns one query row.  (Two threads per row were measured slower on B200 -- 0.418 ms against 0.353 ms on
+// the Llama-3-8B B8 S2048 prefill: the row-max exchange and the register cap of a 576-thread CTA cost more than the
+// extra warps hide -- and so was a variant with P staged in shared memory.)
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -24,10 +34,7 @@ namespace {
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-// Threads per query row in the softmax.  2 was measured slower on B200 (0.418 ms against 0.353 ms on the Llama-3-8B
-// B8 S2048 prefill): the row-max exchange and the 96-register cap of a 576-thread CTA cost more than the extra warps hide.
-constexpr int kHalves = 1;
-constexpr int kThreads = 64 + 2 * 128 * kHalves;  // TMA warp, MMA warp, softmax warps of two query tiles
+constexpr int kThreads = 64 + 2 * 128;  // TMA warp, MMA warp, softmax warps of two query tiles
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;
@@ -38,28 +45,60 @@ template <int D> struct Smem2 {
   static constexpr int kKOff = 2 * kTile;         // two stages
   static constexpr int kVOff = 4 * kTile;         // two stages
   static constexpr int kBarOff = 6 * kTile;
-  static constexpr int kXchOff = kBarOff + 256;   // row max / row sum exchange between the threads of a row
-  static constexpr int kTotal = kXchOff + 6 * 1024 + 1024;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
 struct Attn2Params {
   CUtensorMap map_q, map_k, map_v;
   int B, S, Hq, Hkv, past, kv_len, causal;
+  int n_blocks;      // blocks of 256 queries
+  int n_items;       // n_blocks * kv_splits * Hq * B
   float scale_log2;
   void* o2;
   float* lse2;
-  int kv_splits;     // > 1: the key tiles are dealt out over this many CTAs, which leave partial results
+  int kv_splits;     // > 1: the key tiles are dealt out over this many items, which leave partial results
   float* part_o;     // (kv_splits, B, Hq, S, D) fp32, unnormalised
   float* part_ml;    // (kv_splits, B, Hq, S, 2): exponent reference and row sum of each part
   int* err;
-  long long* trace;  // timing probes (TB200_TRACE builds only)
 };
 
-#ifdef TB200_TRACE
-#define TRACE(slot, cond) do { if ((cond) && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[(slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot, cond) do { } while (0)
-#endif
+// One unit of work.  Items are numbered so that the longest (the last queries of a causal sequence) come first and
+// the q heads that share a kv head are neighbours, i.e. run at the same time on neighbouring SMs.
+struct Item {
+  int q0, hq, b, hkv, sp;
+  int j_begin;   // first key tile of this share
+  int nt[2];     // key tiles of each query tile within the share (0: nothing to do)
+  int nt_max;
+};
+
+__device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
+  Item it;
+  it.nt[0] = it.nt[1] = it.nt_max = 0;
+  it.q0 = it.hq = it.b = it.hkv = it.sp = it.j_begin = 0;
+  if (i >= p.n_items) return it;
+  const int per_blk = p.B * p.Hq * p.kv_splits;
+  const int blk = i / per_blk;
+  int rem = i - blk * per_blk;
+  it.sp = rem % p.kv_splits;
+  rem /= p.kv_splits;
+  it.hq = rem % p.Hq;
+  it.b = rem / p.Hq;
+  it.hkv = it.hq / (p.Hq / p.Hkv);
+  it.q0 = (p.n_blocks - 1 - blk) * 2 * BQ;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0t = it.q0 + t * BQ;
+    int last_key = p.kv_len - 1;
+    if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
+    it.nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
+  }
+  const int per_split = (max(it.nt[0], it.nt[1]) + p.kv_splits - 1) / p.kv_splits;
+  it.j_begin = it.sp * per_split;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) it.nt[t] = max(0, min(it.nt[t], it.j_begin + per_split) - it.j_begin);
+  it.nt_max = max(it.nt[0], it.nt[1]);
+  return it;
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_constant__ Attn2Params p) {
@@ -67,53 +106,34 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2] per query tile
-  uint64_t* p_ready = bars + 11;  // [2] per query tile
-  uint64_t* pv_done = bars + 13;  // [2] per query tile
-  uint64_t* row_xch = bars + 15;  // [2] per query tile: the threads of a row have published their partial
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* q_full = bars + 0;    // [2] per query tile
+  uint64_t* q_empty = bars + 2;   // [2] per query tile: the last S of an item has read Q
+  uint64_t* k_full = bars + 4;    // [2] ring
+  uint64_t* k_empty = bars + 6;
+  uint64_t* v_full = bars + 8;    // [2] ring
+  uint64_t* v_empty = bars + 10;
+  uint64_t* s_full = bars + 12;   // [2] per query tile
+  uint64_t* p_ready = bars + 14;  // [2] per query tile
+  uint64_t* pv_done = bars + 16;  // [2] per query tile
+  uint64_t* o_free = bars + 18;   // [2] per query tile: the warpgroup has read O of the item it finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_blocks = (p.S + 2 * BQ - 1) / (2 * BQ);
-  const int blk = blockIdx.x / p.kv_splits;
-  const int sp = blockIdx.x - blk * p.kv_splits;         // which share of the key tiles this CTA takes
-  const int q0 = (n_blocks - 1 - blk) * 2 * BQ;          // longest blocks first
-  const int hq = blockIdx.y;
-  const int b = blockIdx.z;
-  const int hkv = hq / (p.Hq / p.Hkv);
-  int nt[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int q0t = q0 + t * BQ;
-    int last_key = p.kv_len - 1;
-    if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
-    nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
-  }
-  // key tiles [j_begin, j_begin + nt[t]) of each query tile; local index j below, global j_begin + j for coordinates
-  const int per_split = (max(nt[0], nt[1]) + p.kv_splits - 1) / p.kv_splits;
-  const int j_begin = sp * per_split;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) nt[t] = max(0, min(nt[t], j_begin + per_split) - j_begin);
-  const int nt_max = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128 * kHalves);
+      mbar_init(&p_ready[i], 128);
       mbar_init(&pv_done[i], 1);
-      mbar_init(&row_xch[i], 128 * kHalves);
+      mbar_init(&o_free[i], 128);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -135,34 +155,50 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && nt_max > 0) {
-      mbar_arrive_expect_tx(q_full, 2 * L::kTile);
+    uint32_t ring = 0;               // K/V tiles loaded so far: stage = ring & 1, use = ring >> 1
+    uint32_t q_loads[2] = {0, 0};    // Q tiles loaded so far, per query tile
+    bool ok = true;
+    for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
+      const Item it = decode_item(p, i);
+      // order: Q0, K0, Q1, V0, then K1 V1 K2 V2 ...: the first S of query tile 0 needs only Q0 and K0
+      for (int step = 0; ok && step < 2 * it.nt_max + 2; ++step) {
+        if (step == 0 || step == 2) {
+          const int t = step >> 1;
+          const uint32_t loads = t == 0 ? q_loads[0] : q_loads[1];
+          if ((t == 0 ? it.nt[0] : it.nt[1]) == 0) continue;
+          if (loads > 0 && !mbar_wait(&q_empty[t], (loads - 1) & 1, ctx, 400)) { ok = false; break; }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&q_full[t], L::kTile);
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
+            for (int dc = 0; dc < D / 64; ++dc)
+              tma_load_3d(smem + L::kQOff + t * L::kTile + dc * (BQ * 128), &p.map_q, &q_full[t], dc * 64, it.q0 + t * BQ,
+                          it.b * p.Hq + it.hq);
+          }
+          __syncwarp();
+          if (t == 0) ++q_loads[0]; else ++q_loads[1];
+          continue;
+        }
+        // steps 1, 3, 4, 5, ...  ->  K0, V0, K1, V1, ...
+        const int kv = (step == 1) ? 0 : step - 2;  // 0: K0, 1: V0, 2: K1, ...
+        const int j = kv >> 1;
+        if (j >= it.nt_max) break;
+        const bool is_v = (kv & 1) != 0;
+        const uint32_t pos = ring + static_cast<uint32_t>(j);
+        const uint32_t st = pos & 1, ph = (pos >> 1) & 1;
+        uint64_t* full = is_v ? &v_full[st] : &k_full[st];
+        uint64_t* empty = is_v ? &v_empty[st] : &k_empty[st];
+        if (!mbar_wait(empty, ph ^ 1, ctx, is_v ? 402 : 401)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full, L::kTile);
+          uint8_t* dst = smem + (is_v ? L::kVOff : L::kKOff) + st * L::kTile;
 #pragma unroll
-        for (int dc = 0; dc < D / 64; ++dc)
-          tma_load_3d(smem + L::kQOff + t * L::kTile + dc * (BQ * 128), &p.map_q, q_full, dc * 64, q0 + t * BQ, b * p.Hq + hq);
-    }
-    __syncwarp();
-    for (int j = 0; j < nt_max; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&k_empty[st], ph ^ 1, ctx, 401)) break;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&k_full[st], L::kTile);
-#pragma unroll
-        for (int dc = 0; dc < D / 64; ++dc)
-          tma_load_3d(smem + L::kKOff + st * L::kTile + dc * (BKV * 128), &p.map_k, &k_full[st], dc * 64, (j_begin + j) * BKV, b * p.Hkv + hkv);
+          for (int dc = 0; dc < D / 64; ++dc)
+            tma_load_3d(dst + dc * (BKV * 128), is_v ? &p.map_v : &p.map_k, full, dc * 64, (it.j_begin + j) * BKV,
+                        it.b * p.Hkv + it.hkv);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-      if (!mbar_wait(&v_empty[st], ph ^ 1, ctx, 402)) break;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&v_full[st], L::kTile);
-#pragma unroll
-        for (int dc = 0; dc < D / 64; ++dc)
-          tma_load_3d(smem + L::kVOff + st * L::kTile + dc * (BKV * 128), &p.map_v, &v_full[st], dc * 64, (j_begin + j) * BKV, b * p.Hkv + hkv);
-      }
-      __syncwarp();
+      ring += static_cast<uint32_t>(it.nt_max);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -172,9 +208,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     const uint32_t q_base = smem_u32(smem + L::kQOff);
     const uint32_t k_base = smem_u32(smem + L::kKOff);
     const uint32_t v_base = smem_u32(smem + L::kVOff);
-    auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
+    uint32_t kpos = 0, vpos = 0;      // ring positions of the next K tile an S reads / the next V tile a P V reads
+    uint32_t q_uses[2] = {0, 0};      // items whose Q tile has been waited for, per query tile
+    uint32_t pv_count[2] = {0, 0};    // P V products issued, per query tile (= index of the next P)
+    uint32_t o_items[2] = {0, 0};     // items that have started accumulating into O, per query tile
+    bool ok = true;
+
+    auto issue_s = [&](int t) {  // S_t = Q_t K^T with the K tile at ring position kpos
       const uint64_t qd = make_smem_desc(q_base + t * L::kTile, 16, 1024);
-      const uint64_t kd = make_smem_desc(k_base + (j & 1) * L::kTile, 16, 1024);
+      const uint64_t kd = make_smem_desc(k_base + (kpos & 1) * L::kTile, 16, 1024);
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);  // start-address field
@@ -182,204 +224,239 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       }
       umma_commit_warp(&s_full[t]);
     };
-    auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j, P_t read from tensor memory
-      const uint64_t vd = make_smem_desc(v_base + (j & 1) * L::kTile, BKV * 128, 1024);
+    auto issue_pv = [&](int t, bool accumulate) {  // O_t (+)= P_t V, P_t read from tensor memory, V at ring position vpos
+      const uint64_t vd = make_smem_desc(v_base + (vpos & 1) * L::kTile, BKV * 128, 1024);
 #pragma unroll
       for (int kk = 0; kk < BKV / 16; ++kk)
         umma_ts_warp(tmem_base + 2 * BKV + t * D, tmem_base + t * BKV + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
-                     (j > 0 || kk > 0) ? 1u : 0u);
+                     (accumulate || kk > 0) ? 1u : 0u);
       umma_commit_warp(&pv_done[t]);
     };
-    bool ok = nt_max > 0 && mbar_wait(q_full, 0, ctx, 403) && mbar_wait(&k_full[0], 0, ctx, 404);
-    if (ok) {
+    bool k_ready = false;
+    auto need_k = [&]() -> bool {  // the K tile at kpos has landed
+      if (k_ready) return true;
+      if (!mbar_wait(&k_full[kpos & 1], (kpos >> 1) & 1, ctx, 407)) return false;
       tc_fence_after();
-      if (nt[0] > 0) issue_s(0, 0);
-      if (nt[1] > 0) issue_s(1, 0);
-      umma_commit_warp(&k_empty[0]);
-    }
-    for (int j = 0; ok && j < nt_max; ++j) {
-      if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, ctx, 405)) break;
-      bool k_ready = false;
+      k_ready = true;
+      return true;
+    };
+    auto k_step_done = [&]() {  // every S that reads the K tile at kpos has been issued
+      if (k_ready) {
+        umma_commit_warp(&k_empty[kpos & 1]);
+        ++kpos;
+        k_ready = false;
+      }
+    };
+    // first S tiles of an item (Q just loaded, first K tile of the item)
+    auto start_item = [&](const Item& it) -> bool {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        if (j < nt[t]) {
-          if (!mbar_wait(&p_ready[t], j & 1, ctx, 406)) { ok = false; break; }
-          tc_fence_after();
-          TRACE(512 + (t * 32 + j) * 4 + 0, lane == 0 && j < 32);
-          issue_pv(t, j);
-          TRACE(512 + (t * 32 + j) * 4 + 1, lane == 0 && j < 32);
-        }
-        if (t == 1) umma_commit_warp(&v_empty[j & 1]);
-        if (j + 1 < nt[t]) {
-          if (!k_ready) {
-            if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, 407)) { ok = false; break; }
-            tc_fence_after();
-            k_ready = true;
-          }
-          issue_s(t, j + 1);
-          TRACE(512 + (t * 32 + j) * 4 + 2, lane == 0 && j < 32);
-        }
+        if (it.nt[t] == 0) continue;
+        if (!mbar_wait(&q_full[t], q_uses[t] & 1, ctx, 403)) return false;
+        ++q_uses[t];
+        if (!need_k()) return false;
+        tc_fence_after();
+        issue_s(t);
+        if (it.nt[t] == 1) umma_commit_warp(&q_empty[t]);
       }
-      if (ok && j + 1 < nt_max) umma_commit_warp(&k_empty[(j + 1) & 1]);
+      k_step_done();
+      return true;
+    };
+    auto do_pv = [&](int t, int j) -> bool {
+      if (j == 0) {
+        if (o_items[t] > 0 && !mbar_wait(&o_free[t], (o_items[t] - 1) & 1, ctx, 410)) return false;
+        ++o_items[t];
+      }
+      if (!mbar_wait(&p_ready[t], pv_count[t] & 1, ctx, 406)) return false;
+      tc_fence_after();
+      issue_pv(t, j > 0);
+      ++pv_count[t];
+      return true;
+    };
+
+    Item cur = decode_item(p, blockIdx.x);
+    ok = start_item(cur);
+    for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
+      const Item nxt = decode_item(p, i + gridDim.x);
+      if (cur.nt_max == 0) ok = start_item(nxt);
+      for (int j = 0; ok && j < cur.nt_max; ++j) {
+        if (!mbar_wait(&v_full[vpos & 1], (vpos >> 1) & 1, ctx, 405)) { ok = false; break; }
+        tc_fence_after();
+        if (j + 1 < cur.nt_max) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (j < cur.nt[t] && !do_pv(t, j)) { ok = false; break; }
+            if (t == 1) umma_commit_warp(&v_empty[vpos & 1]);
+            if (j + 1 < cur.nt[t]) {
+              if (!need_k()) { ok = false; break; }
+              issue_s(t);
+              if (j + 2 == cur.nt[t]) umma_commit_warp(&q_empty[t]);  // that was the item's last read of Q_t
+            }
+          }
+          if (!ok) break;
+          k_step_done();
+        } else {  // last step of the item: both P V first, then the first S tiles of the next item
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            if (j < cur.nt[t] && !do_pv(t, j)) { ok = false; break; }
+          if (!ok) break;
+          umma_commit_warp(&v_empty[vpos & 1]);
+          ok = start_item(nxt);
+        }
+        ++vpos;
+      }
+      cur = nxt;
     }
   } else {
-    // ------------------------------------------------------------ softmax warps
-    // kHalves threads share a query row: thread (row, h) owns the S columns [h*CW, (h+1)*CW) of the row and the O
-    // columns [h*D/kHalves, ...).  The two threads sit in different warps that may touch the same TMEM lanes
-    // (warp % 4 is equal), which doubles the warps per SM sub-partition available to hide MUFU / FMA latency.
-    constexpr int CW = BKV / kHalves;   // S columns per thread
-    constexpr int OW = D / kHalves;     // O columns per thread
-    const int sw = warp - 2;
-    const int t = sw / (4 * kHalves);   // query tile
-    const int h = (sw >> 2) % kHalves;  // column half
-    const int quad = warp & 3;
+    // ------------------------------------------------------------ softmax warps: a thread owns a query row
+    const int t = (warp - 2) >> 2;  // query tile
+    const int quad = warp & 3;      // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
     const int r_in = quad * 32 + lane;
-    const int qi = q0 + t * BQ + r_in;
-    const bool row_ok = qi < p.S;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * BKV + lane_sel;
-    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + h * OW + lane_sel;
-    const int key_limit = p.causal ? min(p.past + qi, p.kv_len - 1) : p.kv_len - 1;
-    const int my_nt = nt[t];
-    float* xmax = reinterpret_cast<float*>(smem + L::kXchOff) + t * (2 * kHalves * 128);  // [parity][half][row]
-    float* xsum = reinterpret_cast<float*>(smem + L::kXchOff) + 2 * (2 * kHalves * 128) + t * (kHalves * 128);
-    float m_use = -INFINITY, l = 0.f;
+    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
+    uint32_t s_count = 0;  // S tiles consumed so far by this query tile, over all items
     bool ok = true;
 
-    for (int j = 0; j < my_nt; ++j) {
-      const int k0 = (j_begin + j) * BKV + h * CW;
-      TRACE((t * 32 + j) * 8 + 0, r_in == 0 && h == 0 && j < 32);
-      if (!mbar_wait(&s_full[t], j & 1, ctx, 408)) { ok = false; break; }
-      tc_fence_after();
-      TRACE((t * 32 + j) * 8 + 1, r_in == 0 && h == 0 && j < 32);
-      uint32_t s[CW];
-#pragma unroll
-      for (int c = 0; c < CW / 32; ++c) tmem_ld_x32(tmem_s + h * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-      tmem_wait_ld();
-      TRACE((t * 32 + j) * 8 + 2, r_in == 0 && h == 0 && j < 32);
+    for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
+      int my_nt, k_first, key_limit;
+      {  // only what the key loop needs stays live through it; the item is decoded again for the output addresses
+        const Item it = decode_item(p, i);
+        my_nt = t == 0 ? it.nt[0] : it.nt[1];
+        k_first = it.j_begin * BKV;
+        const int qi = it.q0 + t * BQ + r_in;
+        key_limit = p.causal ? min(p.past + qi, p.kv_len - 1) : p.kv_len - 1;
+      }
+      float m_use = -INFINITY, l = 0.f;
 
-      if (k0 + CW - 1 > key_limit) {  // these columns touch the causal diagonal or the end of the keys
+      for (int j = 0; j < my_nt; ++j, ++s_count) {
+        const int k0 = k_first + j * BKV;
+        if (!mbar_wait(&s_full[t], s_count & 1, ctx, 408)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[BKV];
 #pragma unroll
-        for (int i = 0; i < CW; ++i)
-          if (k0 + i > key_limit) s[i] = 0xff800000u;  // -inf
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < CW; i += 8) {  // three-input max: one instruction per two elements, four chains
-        mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-      }
-      float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      if (kHalves > 1) {  // combine with the other half of the row (bounded wait, no bar.sync)
-        float* slot = xmax + (j & 1) * (kHalves * 128);
-        slot[h * 128 + r_in] = rowmax;
-        mbar_arrive(&row_xch[t]);
-        if (!mbar_wait(&row_xch[t], j & 1, ctx, 410)) { ok = false; break; }
-        rowmax = fmaxf(rowmax, slot[(h ^ 1) * 128 + r_in]);
-      }
-      const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
-      const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
-      float alpha = 1.f;
-      if (grow) {
-        alpha = fast_exp2(m_use - m_new);
-        m_use = m_new;
-      }
-      const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
-      TRACE((t * 32 + j) * 8 + 3, r_in == 0 && h == 0 && j < 32);
-      // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-      const float2 nm2 = make_float2(neg_mref, neg_mref);
-      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-      uint32_t pk[CW / 2];
-#pragma unroll
-      for (int i = 0; i < CW; i += 4) {
-        const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nm2);
-        const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, nm2);
-        const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
-        const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
-        acc0 = __fadd2_rn(acc0, e0);
-        acc1 = __fadd2_rn(acc1, e1);
-        pk[i >> 1] = Pack2<T>::pack(e0.x, e0.y);
-        pk[(i >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
-      }
-      l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));  // this thread's share of the row sum
-      TRACE((t * 32 + j) * 8 + 4, r_in == 0 && h == 0 && j < 32);
+        for (int c = 0; c < BKV / 32; ++c) tmem_ld_x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+        tmem_wait_ld();
 
-      // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        if (k0 + BKV - 1 > key_limit) {  // these columns touch the causal diagonal or the end of the keys
+#pragma unroll
+          for (int c = 0; c < BKV; ++c)
+            if (k0 + c > key_limit) s[c] = 0xff800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < BKV; c += 8) {  // three-input max: one instruction per two elements, four chains
+          mx0 = max3(mx0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+        }
+        const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
+        const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
+        float alpha = 1.f;
+        if (grow) {
+          alpha = fast_exp2(m_use - m_new);
+          m_use = m_new;
+        }
+        const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
+        // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 nm2 = make_float2(neg_mref, neg_mref);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+        uint32_t pk[BKV / 2];
+#pragma unroll
+        for (int c = 0; c < BKV; c += 4) {
+          const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, nm2);
+          const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sc2, nm2);
+          const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+          const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+          acc0 = __fadd2_rn(acc0, e0);
+          acc1 = __fadd2_rn(acc1, e1);
+          pk[c >> 1] = Pack2<T>::pack(e0.x, e0.y);
+          pk[(c >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
+        }
+        l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
+
+        // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          uint32_t o[32];
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld_x32(tmem_o + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_x32(tmem_o + c * 32, o);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < BKV / 64; ++c)  // 64 keys = 32 packed columns per store
+          tmem_st_x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[c * 32]));
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_ready[t]);
+      }
+      if (!ok) break;
+
+      // ---- end of the item: O leaves tensor memory first (which lets the next item's P V start), then goes out
+      const bool have = my_nt > 0 && mbar_wait(&pv_done[t], (s_count - 1) & 1, ctx, 409);
+      if (my_nt > 0 && !have) { ok = false; break; }
+      const Item it = decode_item(p, i);
+      const int qi = it.q0 + t * BQ + r_in;
+      const bool row_ok = qi < p.S;
+      if (p.kv_splits > 1) {
+        // this item saw only a share of the keys: leave the unnormalised accumulator, its exponent reference and its
+        // row sum; attn_combine_kernel merges the shares.  A share without keys leaves the neutral element.
+        const long long prow = ((static_cast<long long>(it.sp) * p.B + it.b) * p.Hq + it.hq) * p.S + qi;
+        if (have) tc_fence_after();
         uint32_t o[32];
 #pragma unroll 1
-        for (int c = 0; c < OW / 32; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
+          if (have) {  // uniform over the warp
+            tmem_ld_x32(tmem_o + c * 32, o);
+            tmem_wait_ld();
+            if (c == D / 32 - 1) {
+              tc_fence_before();
+              mbar_arrive(&o_free[t]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+          if (row_ok) {
+            uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D + c * 32);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
+          }
+        }
+        if (row_ok) {
+          p.part_ml[prow * 2] = have ? m_use : -INFINITY;
+          p.part_ml[prow * 2 + 1] = have ? l : 0.f;
+        }
+      } else if (have) {
+        tc_fence_after();
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        uint32_t packed[D / 2];
+        uint32_t o[32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
           tmem_ld_x32(tmem_o + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_x32(tmem_o + c * 32, o);
+          for (int e = 0; e < 16; ++e)
+            packed[c * 16 + e] = Pack2<T>::pack(__uint_as_float(o[2 * e]) * inv_l, __uint_as_float(o[2 * e + 1]) * inv_l);
         }
-      }
-#pragma unroll
-      for (int c = 0; c < CW / 64; ++c)  // 64 keys = 32 packed columns per store
-        tmem_st_x32(tmem_s + h * (CW / 2) + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[c * 32]));
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_ready[t]);
-      TRACE((t * 32 + j) * 8 + 5, r_in == 0 && h == 0 && j < 32);
-    }
-
-    if (ok && my_nt > 0 && kHalves > 1) {  // total row sum
-      xsum[h * 128 + r_in] = l;
-      mbar_arrive(&row_xch[t]);
-      ok = mbar_wait(&row_xch[t], my_nt & 1, ctx, 411);
-      if (ok) l += xsum[(h ^ 1) * 128 + r_in];
-    }
-    if (p.kv_splits > 1) {
-      // this CTA saw only a share of the keys: leave the unnormalised accumulator, its exponent reference and its row
-      // sum; attn_combine_kernel merges the shares.  A share without keys leaves the neutral element.
-      const long long prow = ((static_cast<long long>(sp) * p.B + b) * p.Hq + hq) * p.S + qi;
-      const bool have = ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409);
-      if (have) tc_fence_after();
-      uint32_t o[32];
-#pragma unroll 1
-      for (int c = 0; c < OW / 32; ++c) {
-        if (have) {  // uniform over the warp
-          tmem_ld_x32(tmem_o + c * 32, o);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
+        tc_fence_before();
+        mbar_arrive(&o_free[t]);
         if (row_ok) {
-          uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D + h * OW + c * 32);
+          T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(it.b) * p.S + qi) * p.Hq + it.hq) * D;
+          uint4* d = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) d[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          for (int e = 0; e < D / 8; ++e) d[e] = make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]);
+          if (p.lse2 != nullptr) p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
         }
       }
-      if (row_ok && h == 0) {
-        p.part_ml[prow * 2] = have ? m_use : -INFINITY;
-        p.part_ml[prow * 2 + 1] = have ? l : 0.f;
-      }
-    } else if (ok && my_nt > 0 && mbar_wait(&pv_done[t], (my_nt - 1) & 1, ctx, 409)) {
-      tc_fence_after();
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(b) * p.S + qi) * p.Hq + hq) * D + h * OW;
-      uint32_t o[32];
-#pragma unroll 1
-      for (int c = 0; c < OW / 32; ++c) {
-        tmem_ld_x32(tmem_o + c * 32, o);
-        tmem_wait_ld();
-        if (row_ok) {
-          uint4* d = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            d[i] = make_uint4(Pack2<T>::pack(__uint_as_float(o[8 * i]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l),
-                              Pack2<T>::pack(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l),
-                              Pack2<T>::pack(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l),
-                              Pack2<T>::pack(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l));
-        }
-      }
-      if (row_ok && h == 0 && p.lse2 != nullptr) p.lse2[(static_cast<long long>(b) * p.Hq + hq) * p.S + qi] = m_use + log2f(l);
     }
   }
 
@@ -476,9 +553,6 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.part_o = a.part_o;
   p.part_ml = a.part_ml;
   p.err = st->err_word;
-#ifdef TB200_TRACE
-  if (const char* tp = getenv("TB200_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(tp, nullptr, 0));
-#endif
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
@@ -493,7 +567,11 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
     if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
   }
-  const dim3 grid(((a.S + 2 * BQ - 1) / (2 * BQ)) * p.kv_splits, a.Hq, a.B);
+  p.n_blocks = (a.S + 2 * BQ - 1) / (2 * BQ);
+  const long long items = static_cast<long long>(p.n_blocks) * p.kv_splits * a.Hq * a.B;
+  if (items > 0x7fffffffLL) return TB200_ERR_INVALID;
+  p.n_items = static_cast<int>(items);
+  const dim3 grid(static_cast<unsigned>(p.n_items < st->num_sms ? p.n_items : st->num_sms), 1, 1);  // persistent: one CTA per SM
   if (a.dtype == TB200_BF16) {
     return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
   }
