@@ -131,9 +131,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 4);   // one arrival per warp of the warpgroup
       mbar_init(&pv_done[i], 1);
-      mbar_init(&o_free[i], 128);
+      mbar_init(&o_free[i], 4);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -395,7 +395,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           tmem_st_x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[c * 32]));
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_ready[t]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);  // arrivals on one barrier serialise: one per warp, not per thread
       }
       if (!ok) break;
 
@@ -418,7 +419,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
             tmem_wait_ld();
             if (c == D / 32 - 1) {
               tc_fence_before();
-              mbar_arrive(&o_free[t]);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&o_free[t]);
             }
           } else {
 #pragma unroll
@@ -448,7 +450,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
             packed[c * 16 + e] = Pack2<T>::pack(__uint_as_float(o[2 * e]) * inv_l, __uint_as_float(o[2 * e + 1]) * inv_l);
         }
         tc_fence_before();
-        mbar_arrive(&o_free[t]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_free[t]);
         if (row_ok) {
           T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(it.b) * p.S + qi) * p.Hq + it.hq) * D;
           uint4* d = reinterpret_cast<uint4*>(orow);

@@ -6,10 +6,16 @@
 //
 // One CTA per (128-key tile, q head, batch element).  The scores are recomputed TRANSPOSED on the tensor
 // core, S^T = K_tile Q_i^T, so that a TMEM lane is a key and its columns are the queries: the sum over
-// queries is then a thread-local loop -- no atomics, no cross-thread reduction, run-to-run identical.
-//   warp 0     TMA: the K tile once, then the Q tiles that can see it (two-deep ring)
-//   warp 1     MMA: S^T into two 128-column TMEM buffers
-//   warps 2-5  reduction: thread = key; log-sum-exp of the 128 queries of the tile staged in shared memory
+// queries is then a thread-local loop -- no atomics, run-to-run identical.
+//   warp 0      TMA: the K tile once, then the Q tiles that can see it (two-deep ring)
+//   warp 1      MMA: S^T into four 128-column TMEM buffers (two per reducer group)
+//   warp 2      TMA (KeyFormer): the noise tiles through a ring of their own, three or four deep -- the pass
+//               streams the noise tensor, so enough of it must be in flight, and its waits must not hold up Q
+//   warps 4-19  reduction, in two groups of eight warps that take alternate query tiles: thread = (key, half of the
+//               tile's queries).  The groups run out of step, so while one waits for its next S^T tile, copies row
+//               statistics or loads from tensor memory, the other keeps the special-function unit busy (with all
+//               warps in step those phases were measured to cost as much as the exponentials).  Partial sums are
+//               added in a fixed order at the end.
 #include <math.h>
 #include <string.h>
 
@@ -22,19 +28,23 @@ namespace {
 
 constexpr int BK_ = 128;  // keys per CTA
 constexpr int BQ_ = 128;  // queries per step
-constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
+constexpr int kReducers = 512;
+constexpr int kThreads = 128 + kReducers;  // warps 0..3: K/Q producer, MMA issuer, noise producer, idle
+constexpr int kTmemCols = 512;  // four S^T buffers
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D, bool NOISE> struct ScoreSmem {
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kNoiseBytes = 128 * 128 * 2;              // [2 chunks of 64 keys][128 queries][128 B], swizzled
+  static constexpr int kNoiseStages = (D == 128) ? 3 : 4;        // what fits beside K and the Q ring
+  static constexpr int kQStages = (NOISE && D == 128) ? 2 : 4;
   static constexpr int kKOff = 0;
   static constexpr int kQOff = kTileBytes;
-  static constexpr int kNoiseOff = kQOff + 2 * kTileBytes;       // two-deep ring (KeyFormer only)
-  static constexpr int kLseOff = kNoiseOff + (NOISE ? 2 * kNoiseBytes : 0);  // [2 buffers][2 statistics][128] fp32
-  static constexpr int kBarOff = kLseOff + 2 * 2 * 128 * 4;
-  static constexpr int kTotal = kBarOff + 128 + 1024;
+  static constexpr int kNoiseOff = kQOff + kQStages * kTileBytes;  // ring (KeyFormer only)
+  static constexpr int kLseOff = kNoiseOff + (NOISE ? kNoiseStages * kNoiseBytes : 0);  // [8 buffers][2 statistics][128] fp32
+  static constexpr int kRedOff = kLseOff + 8 * 2 * 128 * 4;      // [3 sums][4 partial sums][128 keys] fp32
+  static constexpr int kBarOff = kRedOff + 3 * 4 * 128 * 4;
+  static constexpr int kTotal = kBarOff + 512 + 1024;
 };
 
 struct ScoreParams {
@@ -53,24 +63,28 @@ struct ScoreParams {
   int* err;
 };
 
-__device__ __forceinline__ void bar_sync_reducers() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
 template <typename T, int D, bool NOISE>
-__global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constant__ ScoreParams p) {
+__global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constant__ ScoreParams p) {
   using L = ScoreSmem<D, NOISE>;
+  constexpr int kNoiseStages = L::kNoiseStages;
+  constexpr int QS = L::kQStages;
+  constexpr int kPrefetch = 6;  // tiles asked into L2 ahead of the ring
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* k_full = bars + 0;
-  uint64_t* q_full = bars + 1;   // [2]
-  uint64_t* q_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;   // [2]
-  uint64_t* s_empty = bars + 7;  // [2]
-  uint64_t* n_full = bars + 9;   // [2] noise tiles
-  uint64_t* n_empty = bars + 11; // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* q_full = bars + 1;   // [QS]
+  uint64_t* q_empty = bars + 5;  // [QS]
+  uint64_t* s_full = bars + 9;   // [4]
+  uint64_t* s_empty = bars + 13; // [4]
+  uint64_t* n_full = bars + 17;  // [kNoiseStages] noise tiles
+  uint64_t* n_empty = bars + 17 + kNoiseStages;
+  uint64_t* lse_ready = bars + 17 + 2 * kNoiseStages;  // [8] the row statistics of a query tile are staged
+  uint64_t* red_done = lse_ready + 8;                 // every reducer has published its partial sums
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* lse_s = reinterpret_cast<float*>(smem + L::kLseOff);
+  float* red_s = reinterpret_cast<float*>(smem + L::kRedOff);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -79,21 +93,27 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
   const int b = blockIdx.z;
   const int hkv = hq / (p.Hq / p.Hkv);
   const int q_tiles = (p.S + BQ_ - 1) / BQ_;
-  // first query tile that can see key k0+127 ... any key of this tile: query i sees key j iff j <= past + i
+  // first query tile that can see any key of this tile: query i sees key j iff j <= past + i
   int first_tile = 0;
   if (p.causal && k0 > p.past) first_tile = (k0 - p.past) / BQ_;
   const int nt = q_tiles - first_tile;
 
   if (threadIdx.x == 0) {
     mbar_init(k_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < QS; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
-      mbar_init(&n_full[i], 1);
-      mbar_init(&n_empty[i], 128);
     }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], kReducers / 64);  // one arrival per warp of the group that owns the tile
+    }
+    for (int i = 0; i < kNoiseStages; ++i) {
+      mbar_init(&n_full[i], 1);
+      mbar_init(&n_empty[i], kReducers / 64);
+    }
+    for (int i = 0; i < 8; ++i) mbar_init(&lse_ready[i], NOISE ? 8 : 4);  // staging warps of the owning group
+    mbar_init(red_done, kReducers / 32);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -115,20 +135,16 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
         tma_load_3d(smem + L::kKOff + dc * (128 * 128), &p.map_k, k_full, dc * 64, k0, b * p.Hkv + hkv);
     }
     __syncwarp();
-    for (int i = 0; i < nt; ++i) {
-      const int st = i & 1;
-      if (NOISE && p.noise_tma) {
-        if (!mbar_wait(&n_empty[st], ((i >> 1) & 1) ^ 1, ctx, 306)) break;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&n_full[st], L::kNoiseBytes);
+    if (lane == 0)
+      for (int i = 0; i < min(nt, kPrefetch); ++i)
 #pragma unroll
-          for (int kc = 0; kc < 2; ++kc)
-            tma_load_3d(smem + L::kNoiseOff + st * L::kNoiseBytes + kc * (128 * 128), &p.map_noise, &n_full[st], k0 + kc * 64,
-                        (first_tile + i) * BQ_, b * p.Hq + hq);
-        }
-        __syncwarp();
-      }
-      if (!mbar_wait(&q_empty[st], ((i >> 1) & 1) ^ 1, ctx, 301)) break;
+        for (int dc = 0; dc < D / 64; ++dc) tma_prefetch_l2_3d(&p.map_q, dc * 64, (first_tile + i) * BQ_, b * p.Hq + hq);
+    for (int i = 0; i < nt; ++i) {
+      const int st = i % QS;
+      if (lane == 0 && i + kPrefetch < nt)
+#pragma unroll
+        for (int dc = 0; dc < D / 64; ++dc) tma_prefetch_l2_3d(&p.map_q, dc * 64, (first_tile + i + kPrefetch) * BQ_, b * p.Hq + hq);
+      if (!mbar_wait(&q_empty[st], ((i / QS) & 1) ^ 1, ctx, 301)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&q_full[st], L::kTileBytes);
 #pragma unroll
@@ -138,93 +154,202 @@ __global__ void __launch_bounds__(kThreads, 2) score_kernel(const __grid_constan
       }
       __syncwarp();
     }
+  } else if (warp == 2) {
+    if (NOISE && p.noise_tma) {
+      if (lane == 0)
+        for (int i = 0; i < min(nt, kPrefetch); ++i)
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc) tma_prefetch_l2_3d(&p.map_noise, k0 + kc * 64, (first_tile + i) * BQ_, b * p.Hq + hq);
+      for (int i = 0; i < nt; ++i) {
+        const int st = i % kNoiseStages;
+        if (lane == 0 && i + kPrefetch < nt)
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc) tma_prefetch_l2_3d(&p.map_noise, k0 + kc * 64, (first_tile + i + kPrefetch) * BQ_, b * p.Hq + hq);
+        if (!mbar_wait(&n_empty[st], ((i / kNoiseStages) & 1) ^ 1, ctx, 306)) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&n_full[st], L::kNoiseBytes);
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc)
+            tma_load_3d(smem + L::kNoiseOff + st * L::kNoiseBytes + kc * (128 * 128), &p.map_noise, &n_full[st], k0 + kc * 64,
+                        (first_tile + i) * BQ_, b * p.Hq + hq);
+        }
+        __syncwarp();
+      }
+    }
   } else if (warp == 1) {
     constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, false, false, BK_, BQ_);
     const uint32_t k_s = smem_u32(smem + L::kKOff);
     bool ok = mbar_wait(k_full, 0, ctx, 302);
     for (int i = 0; ok && i < nt; ++i) {
-      const int st = i & 1;
-      const uint32_t ph = (i >> 1) & 1;
-      if (!mbar_wait(&q_full[st], ph, ctx, 303)) break;
+      const int st = i & 3;
+      const int qs = i % QS;
+      const uint32_t ph = (i >> 2) & 1;
+      if (!mbar_wait(&q_full[qs], (i / QS) & 1, ctx, 303)) break;
       if (!mbar_wait(&s_empty[st], ph ^ 1, ctx, 304)) break;
       tc_fence_after();
       {  // all lanes converged, operands warp-uniform, one elected lane issues
         const uint64_t kd = make_smem_desc(k_s, 16, 1024);
-        const uint64_t qd = make_smem_desc(smem_u32(smem + L::kQOff + st * L::kTileBytes), 16, 1024);
+        const uint64_t qd = make_smem_desc(smem_u32(smem + L::kQOff + qs * L::kTileBytes), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);
           umma_ss_warp(tmem_base + st * BQ_, kd + off, qd + off, idesc, kk > 0 ? 1u : 0u);
         }
         umma_commit_warp(&s_full[st]);
-        umma_commit_warp(&q_empty[st]);
+        umma_commit_warp(&q_empty[qs]);
       }
     }
-  } else {
-    const int quad = warp & 3;
-    const int r_in = quad * 32 + lane;
+  } else if (warp >= 4) {
+    const int quad = warp & 3;          // quarter of the TMEM lanes (keys) this warp may read
+    const int grp = ((warp - 4) >> 2) & 1;  // which tiles this warp takes: i = grp, grp + 2, ...
+    const int half = (warp - 4) >> 3;       // which 64 of the tile's 128 query columns it sums
+    const int cg = grp * 2 + half;          // slot of its partial sums
+    const int r_in = quad * 32 + lane;  // key within the tile
+    const int rt = half * 128 + r_in;   // thread index within the group, 0..255
     const int kj = k0 + r_in;
     const bool key_ok = kj < p.kv_len;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const long long head_row0 = (static_cast<long long>(b) * p.Hq + hq) * p.S;
+    const float nscale = kLog2e * p.inv_tau;
+    const float st_scale = p.scale_log2 * p.inv_tau;
     float acc_p = 0.f, acc_p2 = 0.f, acc_pt = 0.f;
-    for (int i = 0; i < nt; ++i) {
-      const int st = i & 1;
+    // Threads 0..127 of a group stage lse2 of its tile's queries, threads 128..255 the perturbed statistic (KeyFormer).
+    // +inf for rows past the end makes their probability 0.
+    // Buffer i & 7 is written again for tile i+8 by the same group.  A warp that is there has been handed the S^T
+    // buffer of tile i+6, which is given out only after every warp of the group released tile i+2: all of them are
+    // done with tile i, and no warp runs more than one phase of a buffer's barrier ahead of another.
+    const bool stager = rt < (NOISE ? 256 : 128);
+    const float* stat_src = (rt < 128) ? p.lse2 : p.lse2t;
+    const int stat_row = rt & 127;
+    auto fetch_stat = [&](int tile) -> float {
+      const int qi = (first_tile + tile) * BQ_ + stat_row;
+      return (qi < p.S) ? stat_src[head_row0 + qi] : INFINITY;
+    };
+    // fetched three tiles ahead: a tile takes about as long as one trip to L2, so one tile of lead would expose it
+    float stat0 = (stager && nt > grp) ? fetch_stat(grp) : 0.f;
+    float stat1 = (stager && nt > grp + 2) ? fetch_stat(grp + 2) : 0.f;
+    float stat2 = (stager && nt > grp + 4) ? fetch_stat(grp + 4) : 0.f;
+    for (int i = grp; i < nt; i += 2) {
+      const int st = i & 3;
+      const int lb = i & 7;
       const int q0 = (first_tile + i) * BQ_;
-      // stage the row statistics of this query tile (thread r loads query q0+r)
-      {
-        const int qi = q0 + r_in;
-        lse_s[(st * 2 + 0) * 128 + r_in] = (qi < p.S) ? p.lse2[head_row0 + qi] : INFINITY;  // +inf -> p = 0
-        if (NOISE) lse_s[(st * 2 + 1) * 128 + r_in] = (qi < p.S) ? p.lse2t[head_row0 + qi] : INFINITY;
+      if (stager) {
+        lse_s[(lb * 2 + (rt >> 7)) * 128 + stat_row] = stat0;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&lse_ready[lb]);  // arrivals on one barrier serialise: one per warp
+        stat0 = stat1;
+        stat1 = stat2;
+        if (i + 6 < nt) stat2 = fetch_stat(i + 6);
       }
-      bar_sync_reducers();
-      if (!mbar_wait(&s_full[st], (i >> 1) & 1, ctx, 305)) break;
+      if (!mbar_wait(&s_full[st], (i >> 2) & 1, ctx, 305)) break;
       tc_fence_after();
+      if (!mbar_wait(&lse_ready[lb], (i >> 3) & 1, ctx, 308)) break;
+      const int ns = i % kNoiseStages;
       if (NOISE && p.noise_tma) {
-        if (!mbar_wait(&n_full[st], (i >> 1) & 1, ctx, 307)) break;
+        if (!mbar_wait(&n_full[ns], (i / kNoiseStages) & 1, ctx, 307)) break;
       }
-      // this key's column of the swizzled noise tile: element (query c, key r_in)
-      const uint8_t* n_col = smem + L::kNoiseOff + st * L::kNoiseBytes + (r_in >> 6) * (128 * 128) + (r_in & 7) * 2;
-      const int n_unit = (r_in & 63) >> 3;
-      const float nscale = kLog2e * p.inv_tau;
-      const float* lse_q = lse_s + (st * 2 + 0) * 128;
-      const float* lse_t = lse_s + (st * 2 + 1) * 128;
-      // a query column c is visible to this key iff kj <= past + q0 + c
-      const int c_min = p.causal ? max(0, kj - p.past - q0) : 0;
 #pragma unroll 1
-      for (int cc = 0; cc < BQ_ / 32; ++cc) {
+      for (int ch = 0; ch < 2; ++ch) {  // this warp's 64 query columns, 32 at a time
+        const int cb = half * 64 + ch * 32;
         uint32_t s[32];
-        tmem_ld_x32(tmem_base + st * BQ_ + lane_sel + cc * 32, s);
-        tmem_wait_ld();
+        tmem_ld_x32(tmem_base + st * BQ_ + lane_sel + cb, s);
+        // this key's column of the swizzled noise tile: element (query c, key r_in)
+        const uint8_t* n_col = smem + L::kNoiseOff + ns * L::kNoiseBytes + (r_in >> 6) * (128 * 128) + (cb) * 128 + (r_in & 7) * 2;
+        const int n_unit = (r_in & 63) >> 3;
+        float4 lq4[8];  // the statistic of these 32 queries
+        {
+          const float4* src = reinterpret_cast<const float4*>(lse_s + (lb * 2 + (NOISE ? 1 : 0)) * 128 + cb);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int c = cc * 32 + e;
-          const bool vis = key_ok && (c >= c_min);
-          const float t = __uint_as_float(s[e]) * p.scale_log2;
-          if (!NOISE) {  // RoCo: sums of p and p^2
-            const float pr = vis ? fast_exp2(t - lse_q[c]) : 0.f;
-            acc_p += pr;
-            acc_p2 = fmaf(pr, pr, acc_p2);
-          } else {       // KeyFormer: only the perturbed probability is summed
-            float nz = 0.f;
-            if (p.noise_tma)
-              nz = static_cast<float>(*reinterpret_cast<const T*>(n_col + c * 128 + ((n_unit ^ (c & 7)) << 4)));
-            else if (vis && (q0 + c) < p.S)
-              nz = static_cast<float>(static_cast<const T*>(p.noise)[(head_row0 + q0 + c) * p.kv_len + kj]);
-            const float pt = vis ? fast_exp2(fmaf(nz, nscale, fmaf(t, p.inv_tau, -lse_t[c]))) : 0.f;
-            acc_pt += pt;
+          for (int e4 = 0; e4 < 8; ++e4) lq4[e4] = src[e4];
+        }
+        // query column c of the tile is visible to this key iff kj <= past + q0 + c; only tiles on the diagonal mask
+        const int c_min = (p.causal ? kj - p.past - q0 : 0) - cb;
+        const bool mask_tile = !key_ok || c_min > 0;
+        tmem_wait_ld();
+        if (ch == 1) {  // the last of this warp's S^T columns is in registers: the buffer may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[st]);
+        }
+        // Tiles off the causal diagonal (and with all keys valid) take the branch without per-element tests; the
+        // arithmetic is packed two queries per instruction.  Sums run over fixed positions: identical from run to run.
+        const bool plain = !__any_sync(0xffffffffu, mask_tile) && (!NOISE || p.noise_tma);
+        if (plain) {
+          float2 a1 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float2 nl[2] = {make_float2(-lq4[e4].x, -lq4[e4].y), make_float2(-lq4[e4].z, -lq4[e4].w)};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int e = e4 * 4 + u * 2;
+              const float2 sv = make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+              float2 x;
+              if (!NOISE) {
+                x = __ffma2_rn(sv, make_float2(p.scale_log2, p.scale_log2), nl[u]);
+              } else {
+                const float2 nz = make_float2(
+                    static_cast<float>(*reinterpret_cast<const T*>(n_col + e * 128 + ((n_unit ^ (e & 7)) << 4))),
+                    static_cast<float>(*reinterpret_cast<const T*>(n_col + (e + 1) * 128 + ((n_unit ^ ((e + 1) & 7)) << 4))));
+                x = __ffma2_rn(nz, make_float2(nscale, nscale), __ffma2_rn(sv, make_float2(st_scale, st_scale), nl[u]));
+              }
+              const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+              a1 = __fadd2_rn(a1, pr);
+              if (!NOISE) a2 = __ffma2_rn(pr, pr, a2);
+            }
+          }
+          if (!NOISE) {
+            acc_p += a1.x + a1.y;
+            acc_p2 += a2.x + a2.y;
+          } else {
+            acc_pt += a1.x + a1.y;
+          }
+        } else {
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float lq[4] = {lq4[e4].x, lq4[e4].y, lq4[e4].z, lq4[e4].w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e = e4 * 4 + u;
+              const float sv = __uint_as_float(s[e]);
+              const bool hidden = !key_ok || e < c_min;
+              if (!NOISE) {  // RoCo: sums of p and p^2
+                const float pr = hidden ? 0.f : fast_exp2(fmaf(sv, p.scale_log2, -lq[u]));
+                acc_p += pr;
+                acc_p2 = fmaf(pr, pr, acc_p2);
+              } else {       // KeyFormer: only the perturbed probability is summed
+                float nz = 0.f;
+                if (p.noise_tma)
+                  nz = static_cast<float>(*reinterpret_cast<const T*>(n_col + e * 128 + ((n_unit ^ (e & 7)) << 4)));
+                else if (!hidden && (q0 + cb + e) < p.S)
+                  nz = static_cast<float>(static_cast<const T*>(p.noise)[(head_row0 + q0 + cb + e) * p.kv_len + kj]);
+                const float pt = hidden ? 0.f : fast_exp2(fmaf(nz, nscale, fmaf(sv, st_scale, -lq[u])));
+                acc_pt += pt;
+              }
+            }
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&s_empty[st]);
-      if (NOISE && p.noise_tma) mbar_arrive(&n_empty[st]);
+      if (NOISE && p.noise_tma) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&n_empty[ns]);
+      }
     }
-    if (key_ok) {
+    // add the four query quarters of every key in a fixed order
+    red_s[(0 * 4 + cg) * 128 + r_in] = acc_p;
+    red_s[(1 * 4 + cg) * 128 + r_in] = acc_p2;
+    red_s[(2 * 4 + cg) * 128 + r_in] = acc_pt;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(red_done);
+    if (cg == 0 && key_ok && mbar_wait(red_done, 0, ctx, 309)) {
       const long long o = (static_cast<long long>(b) * p.Hq + hq) * p.kv_len + kj;
-      if (p.sum_p) p.sum_p[o] = acc_p;
-      if (p.sum_p2) p.sum_p2[o] = acc_p2;
-      if (NOISE && p.sum_pt) p.sum_pt[o] = acc_pt;
+      float t[3];
+#pragma unroll
+      for (int w = 0; w < 3; ++w)
+        t[w] = ((red_s[(w * 4 + 0) * 128 + r_in] + red_s[(w * 4 + 1) * 128 + r_in]) + red_s[(w * 4 + 2) * 128 + r_in]) +
+               red_s[(w * 4 + 3) * 128 + r_in];
+      if (p.sum_p) p.sum_p[o] = t[0];
+      if (p.sum_p2) p.sum_p2[o] = t[1];
+      if (NOISE && p.sum_pt) p.sum_pt[o] = t[2];
     }
   }
 
