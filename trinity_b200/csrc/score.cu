@@ -8,14 +8,16 @@
 // core, S^T = K_tile Q_i^T, so that a TMEM lane is a key and its columns are the queries: the sum over
 // queries is then a thread-local loop -- no atomics, run-to-run identical.
 //   warp 0      TMA: the K tile once, then the Q tiles that can see it (two-deep ring)
-//   warp 1      MMA: S^T into four 128-column TMEM buffers (two per reducer group)
+//   warp 1      MMA: S^T into four 128-column TMEM buffers
 //   warp 2      TMA (KeyFormer): the noise tiles through a ring of their own, three or four deep -- the pass
 //               streams the noise tensor, so enough of it must be in flight, and its waits must not hold up Q
-//   warps 4-19  reduction, in two groups of eight warps that take alternate query tiles: thread = (key, half of the
-//               tile's queries).  The groups run out of step, so while one waits for its next S^T tile, copies row
-//               statistics or loads from tensor memory, the other keeps the special-function unit busy (with all
-//               warps in step those phases were measured to cost as much as the exponentials).  Partial sums are
-//               added in a fixed order at the end.
+//   warps 4-19  reduction, in G groups; group g takes query tiles g, g+G, ...  The groups run out of step, so while
+//               one waits for its next S^T tile, copies row statistics or loads from tensor memory, the others
+//               keep the special-function unit busy (with all warps in step those phases were measured to cost
+//               as much as the exponentials).  RoCo: G = 4 groups of four warps, thread = key.  KeyFormer: G = 2
+//               groups of eight warps, thread = (key, half of the tile's queries) -- a group holds a noise stage
+//               while it works on a tile, and with only three stages the tile has to be finished quickly.
+//               The partial sums are added in a fixed order at the end.
 #include <math.h>
 #include <string.h>
 
@@ -69,6 +71,9 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
   constexpr int kNoiseStages = L::kNoiseStages;
   constexpr int QS = L::kQStages;
   constexpr int kPrefetch = 6;  // tiles asked into L2 ahead of the ring
+  constexpr int G = NOISE ? 2 : 4;        // reducer groups
+  constexpr int kGroupWarps = 16 / G;
+  constexpr int kParts = 4 / G;           // warps of a group that share a quarter of the keys and split the queries
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -83,6 +88,10 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
   uint64_t* red_done = lse_ready + 8;                 // every reducer has published its partial sums
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // Noise tiles whose load has been issued.  The reducer groups run out of step and a ring stage serves tiles of
+  // different groups in turn, so a group could reach the stage's barrier a whole phase early and mistake the
+  // previous tile's completed phase for its own; it first waits here until its tile's phase has been armed.
+  volatile int* noise_issued = abort_flag + 1;
   float* lse_s = reinterpret_cast<float*>(smem + L::kLseOff);
   float* red_s = reinterpret_cast<float*>(smem + L::kRedOff);
 
@@ -106,15 +115,16 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], kReducers / 64);  // one arrival per warp of the group that owns the tile
+      mbar_init(&s_empty[i], kGroupWarps);  // one arrival per warp of the group that owns the tile
     }
     for (int i = 0; i < kNoiseStages; ++i) {
       mbar_init(&n_full[i], 1);
-      mbar_init(&n_empty[i], kReducers / 64);
+      mbar_init(&n_empty[i], kGroupWarps);
     }
-    for (int i = 0; i < 8; ++i) mbar_init(&lse_ready[i], NOISE ? 8 : 4);  // staging warps of the owning group
+    for (int i = 0; i < 8; ++i) mbar_init(&lse_ready[i], kGroupWarps);  // the warps of the owning group
     mbar_init(red_done, kReducers / 32);
     *abort_flag = 0;
+    *noise_issued = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -172,6 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
           for (int kc = 0; kc < 2; ++kc)
             tma_load_3d(smem + L::kNoiseOff + st * L::kNoiseBytes + kc * (128 * 128), &p.map_noise, &n_full[st], k0 + kc * 64,
                         (first_tile + i) * BQ_, b * p.Hq + hq);
+          __threadfence_block();  // the armed barrier phase is visible before the count
+          *noise_issued = i + 1;
         }
         __syncwarp();
       }
@@ -201,11 +213,10 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
     }
   } else if (warp >= 4) {
     const int quad = warp & 3;          // quarter of the TMEM lanes (keys) this warp may read
-    const int grp = ((warp - 4) >> 2) & 1;  // which tiles this warp takes: i = grp, grp + 2, ...
-    const int half = (warp - 4) >> 3;       // which 64 of the tile's 128 query columns it sums
-    const int cg = grp * 2 + half;          // slot of its partial sums
-    const int r_in = quad * 32 + lane;  // key within the tile
-    const int rt = half * 128 + r_in;   // thread index within the group, 0..255
+    const int grp = ((warp - 4) >> 2) % G;   // which tiles this warp takes: i = grp, grp + G, ...
+    const int part = (warp - 4) / (4 * G);   // which of the tile's query columns it sums: [part, part + 1) * 128 / kParts
+    const int cg = grp * kParts + part;      // slot of its partial sums
+    const int r_in = quad * 32 + lane;  // key within the tile; also the query row whose statistics it stages
     const int kj = k0 + r_in;
     const bool key_ok = kj < p.kv_len;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
@@ -213,44 +224,70 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
     const float nscale = kLog2e * p.inv_tau;
     const float st_scale = p.scale_log2 * p.inv_tau;
     float acc_p = 0.f, acc_p2 = 0.f, acc_pt = 0.f;
-    // Threads 0..127 of a group stage lse2 of its tile's queries, threads 128..255 the perturbed statistic (KeyFormer).
-    // +inf for rows past the end makes their probability 0.
+    // The first 128 threads of a group stage lse2 of the queries of the group's tile, the last 128 (the same ones when
+    // the group has four warps) the perturbed statistic of KeyFormer; values are fetched three of the group's tiles
+    // ahead: a tile takes about as long as one trip to L2.  +inf for rows past the end makes their probability 0.
     // Buffer i & 7 is written again for tile i+8 by the same group.  A warp that is there has been handed the S^T
-    // buffer of tile i+6, which is given out only after every warp of the group released tile i+2: all of them are
-    // done with tile i, and no warp runs more than one phase of a buffer's barrier ahead of another.
-    const bool stager = rt < (NOISE ? 256 : 128);
-    const float* stat_src = (rt < 128) ? p.lse2 : p.lse2t;
-    const int stat_row = rt & 127;
-    auto fetch_stat = [&](int tile) -> float {
-      const int qi = (first_tile + tile) * BQ_ + stat_row;
-      return (qi < p.S) ? stat_src[head_row0 + qi] : INFINITY;
+    // buffer of tile i+4, which is given out only after every warp of the group released tile i, i.e. has the
+    // tile's statistics in registers: no warp runs more than one phase of a buffer's barrier ahead of another.
+    const bool stage_a = part == 0, stage_b = NOISE && part == kParts - 1;
+    auto fetch_stat = [&](const float* src, int tile) -> float {
+      const int qi = (first_tile + tile) * BQ_ + r_in;
+      return (tile < nt && qi < p.S) ? src[head_row0 + qi] : INFINITY;
     };
-    // fetched three tiles ahead: a tile takes about as long as one trip to L2, so one tile of lead would expose it
-    float stat0 = (stager && nt > grp) ? fetch_stat(grp) : 0.f;
-    float stat1 = (stager && nt > grp + 2) ? fetch_stat(grp + 2) : 0.f;
-    float stat2 = (stager && nt > grp + 4) ? fetch_stat(grp + 4) : 0.f;
-    for (int i = grp; i < nt; i += 2) {
+    float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sb0 = 0.f, sb1 = 0.f, sb2 = 0.f;
+    if (stage_a) {
+      sa0 = fetch_stat(p.lse2, grp);
+      sa1 = fetch_stat(p.lse2, grp + G);
+      sa2 = fetch_stat(p.lse2, grp + 2 * G);
+    }
+    if (stage_b) {
+      sb0 = fetch_stat(p.lse2t, grp);
+      sb1 = fetch_stat(p.lse2t, grp + G);
+      sb2 = fetch_stat(p.lse2t, grp + 2 * G);
+    }
+    for (int i = grp; i < nt; i += G) {
       const int st = i & 3;
       const int lb = i & 7;
       const int q0 = (first_tile + i) * BQ_;
-      if (stager) {
-        lse_s[(lb * 2 + (rt >> 7)) * 128 + stat_row] = stat0;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&lse_ready[lb]);  // arrivals on one barrier serialise: one per warp
-        stat0 = stat1;
-        stat1 = stat2;
-        if (i + 6 < nt) stat2 = fetch_stat(i + 6);
+      if (stage_a) lse_s[(lb * 2 + 0) * 128 + r_in] = sa0;
+      if (stage_b) lse_s[(lb * 2 + 1) * 128 + r_in] = sb0;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&lse_ready[lb]);  // arrivals on one barrier serialise: one per warp
+      if (stage_a) {
+        sa0 = sa1;
+        sa1 = sa2;
+        sa2 = fetch_stat(p.lse2, i + 3 * G);
+      }
+      if (stage_b) {
+        sb0 = sb1;
+        sb1 = sb2;
+        sb2 = fetch_stat(p.lse2t, i + 3 * G);
       }
       if (!mbar_wait(&s_full[st], (i >> 2) & 1, ctx, 305)) break;
       tc_fence_after();
       if (!mbar_wait(&lse_ready[lb], (i >> 3) & 1, ctx, 308)) break;
       const int ns = i % kNoiseStages;
       if (NOISE && p.noise_tma) {
+        bool armed = *noise_issued > i;
+        if (!armed) {
+          const long long t0 = clock64();
+          while (!(armed = *noise_issued > i)) {
+            if (*ctx.flag) break;
+            if (clock64() - t0 > kWaitLimitCycles) {
+              *ctx.flag = 1;
+              atomicCAS(ctx.gerr, 0, 310);
+              break;
+            }
+          }
+        }
+        if (!armed) break;
+        __threadfence_block();
         if (!mbar_wait(&n_full[ns], (i / kNoiseStages) & 1, ctx, 307)) break;
       }
 #pragma unroll 1
-      for (int ch = 0; ch < 2; ++ch) {  // this warp's 64 query columns, 32 at a time
-        const int cb = half * 64 + ch * 32;
+      for (int ch = 0; ch < G; ++ch) {  // this warp's query columns, 32 at a time
+        const int cb = (part * G + ch) * 32;
         uint32_t s[32];
         tmem_ld_x32(tmem_base + st * BQ_ + lane_sel + cb, s);
         // this key's column of the swizzled noise tile: element (query c, key r_in)
@@ -266,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
         const int c_min = (p.causal ? kj - p.past - q0 : 0) - cb;
         const bool mask_tile = !key_ok || c_min > 0;
         tmem_wait_ld();
-        if (ch == 1) {  // the last of this warp's S^T columns is in registers: the buffer may be overwritten
+        if (ch == G - 1) {  // the last of this warp's S^T columns is in registers: the buffer may be overwritten
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_empty[st]);
