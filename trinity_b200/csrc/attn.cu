@@ -418,9 +418,9 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   if (!aligned16(a.q) || !aligned16(a.k_cache) || !aligned16(a.v_cache) || !aligned16(a.o2) || !aligned16(a.noise)) return TB200_ERR_INVALID;
   if (a.Hq > 65535 || a.B > 65535) return TB200_ERR_INVALID;
   if (!(a.sm_scale > 0.f)) return TB200_ERR_INVALID;  // the row maximum is taken before scaling
-  if (a.noise == nullptr) {
+  {  // the two-tile persistent kernel, except for a noise tensor whose rows are not 16-byte aligned (no TMA tiles)
     static const bool single_tile = getenv("TB200_ATTN_SINGLE_TILE") != nullptr;  // A/B switch for measurements
-    if (!single_tile) return launch_attn_fwd_pingpong(a, stream);
+    if (!single_tile && (a.noise == nullptr || ((a.past + a.S) & 7) == 0)) return launch_attn_fwd_pingpong(a, stream);
   }
 
   AttnParams p;
