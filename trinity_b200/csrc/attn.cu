@@ -420,7 +420,8 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   if (!(a.sm_scale > 0.f)) return TB200_ERR_INVALID;  // the row maximum is taken before scaling
   {  // the two-tile persistent kernel, except for a noise tensor whose rows are not 16-byte aligned (no TMA tiles)
     static const bool single_tile = getenv("TB200_ATTN_SINGLE_TILE") != nullptr;  // A/B switch for measurements
-    if (!single_tile && (a.noise == nullptr || ((a.past + a.S) & 7) == 0)) return launch_attn_fwd_pingpong(a, stream);
+    if (!single_tile && a.noise == nullptr) return launch_attn_fwd_pingpong(a, stream);
+    if (!single_tile && ((a.past + a.S) & 7) == 0) return launch_attn_fwd_keyformer(a, stream);
   }
 
   AttnParams p;

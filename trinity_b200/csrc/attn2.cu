@@ -1,13 +1,12 @@
 // Attention forward, two query tiles per CTA ("ping-pong"): the kernel used when no noise tensor is involved.
 //
 // Persistent: one CTA per SM walks work items (256 queries, q head, batch element[, share of the keys]), longest
-// items first.  384 threads:
-//   warp 0      TMA producer: the two Q tiles of an item, then its K and V tiles of BKV keys through two-deep rings
+// items first.  320 threads:
+//   warp 0      TMA producer: the two Q tiles of an item, then its K and V tiles of 128 keys through two-deep rings
 //               that run on across items
 //   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}; in the last step of
 //               an item the S_0 tiles of the NEXT item take the place of S_{j+1}
-//   warp 2      TMA producer of the noise tiles (KeyFormer only); warp 3 idles
-//   warps 4-7   softmax of query tile 0          warps 8-11  softmax of query tile 1
+//   warps 2-5   softmax of query tile 0          warps 6-9   softmax of query tile 1
 // While one softmax warpgroup works on its S tile the tensor core serves the other tile, and each SM sub-partition
 // holds two softmax warps whose MUFU / FMA / TMEM latencies overlap.  K and V tiles are fetched once for 256 queries.
 // Across items the pipeline does not drain: while a warpgroup normalises and stores O of item i, the Q tiles of item
@@ -18,11 +17,6 @@
 // from tensor memory (no shared-memory round trip).  MMAs issued by one thread complete in issue order, so S_{j+1}
 // (issued after P_j V_j) cannot overwrite P_j early, and an arrival on s_full also means the previous P V is done.
 // The first P V of an item overwrites O, so it waits until the warpgroup has read the previous item's O (o_free).
-//
-// KeyFormer (NOISE): the same pass keeps the online log-sum-exp of (scale*s + noise)/tau per row.  That is two
-// exponentials per score, so the pass is bound by the special-function unit, not by the tensor core: it runs with
-// BKV = 64, which leaves room for a six-deep ring of 128 x 64 noise tiles (the noise tensor is streamed from HBM
-// once, so enough of it has to be in flight).
 //
 // One thread owns one query row.  (Two threads per row were measured slower on B200 -- 0.418 ms against 0.353 ms on
 // the Llama-3-8B B8 S2048 prefill: the row-max exchange and the register cap of a 576-thread CTA cost more than the
@@ -39,31 +33,23 @@ namespace tb200 {
 namespace {
 
 constexpr int BQ = 128;
-constexpr int kThreads = 128 + 2 * 128;  // TMA warp, MMA warp, noise TMA warp, idle warp, softmax warps of two query tiles
-constexpr int kNoiseStages = 6;
+constexpr int BKV = 128;
+constexpr int kThreads = 64 + 2 * 128;  // TMA warp, MMA warp, softmax warps of two query tiles
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;
 
-template <int D, int BKV, bool NOISE> struct Smem2 {
-  static constexpr int kQTile = BQ * D * 2;
-  static constexpr int kKVTile = BKV * D * 2;
-  static constexpr int kNoiseTile = BQ * BKV * 2;                 // [128 queries][128 B] swizzled; BKV = 64 with noise
-  static constexpr int kQOff = 0;                                 // two query tiles
-  static constexpr int kKOff = 2 * kQTile;                        // two stages
-  static constexpr int kVOff = kKOff + 2 * kKVTile;               // two stages
-  static constexpr int kNoiseOff = kVOff + 2 * kKVTile;           // ring (KeyFormer only)
-  static constexpr int kBarOff = kNoiseOff + (NOISE ? kNoiseStages * kNoiseTile : 0);
-  static constexpr int kTotal = kBarOff + 512 + 1024;
-  static_assert(!NOISE || BKV == 64, "a noise tile is one 128-byte-wide swizzled block");
+template <int D> struct Smem2 {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kQOff = 0;                 // two query tiles
+  static constexpr int kKOff = 2 * kTile;         // two stages
+  static constexpr int kVOff = 4 * kTile;         // two stages
+  static constexpr int kBarOff = 6 * kTile;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
 struct Attn2Params {
   CUtensorMap map_q, map_k, map_v;
-  CUtensorMap map_noise;       // dims {past+S, S, B*Hq}, box {64, 128, 1} (KeyFormer)
-  int bkv;                     // keys per step of the kernel this launch uses
-  float inv_tau;
-  float* lse2_perturbed;       // (B,Hq,S): log2-domain log-sum-exp of (scale*s + noise)/tau
   int B, S, Hq, Hkv, past, kv_len, causal;
   int n_blocks;      // blocks of 256 queries
   int n_items;       // n_blocks * kv_splits * Hq * B
@@ -104,7 +90,7 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
     const int q0t = it.q0 + t * BQ;
     int last_key = p.kv_len - 1;
     if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
-    it.nt[t] = (q0t < p.S) ? last_key / p.bkv + 1 : 0;
+    it.nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
   }
   const int per_split = (max(it.nt[0], it.nt[1]) + p.kv_splits - 1) / p.kv_splits;
   it.j_begin = it.sp * per_split;
@@ -114,9 +100,9 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
   return it;
 }
 
-template <typename T, int D, int BKV, bool NOISE>
+template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_constant__ Attn2Params p) {
-  using L = Smem2<D, BKV, NOISE>;
+  using L = Smem2<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -130,14 +116,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   uint64_t* p_ready = bars + 14;  // [2] per query tile
   uint64_t* pv_done = bars + 16;  // [2] per query tile
   uint64_t* o_free = bars + 18;   // [2] per query tile: the warpgroup has read O of the item it finished
-  uint64_t* n_full = bars + 20;   // [kNoiseStages]
-  uint64_t* n_empty = bars + 20 + kNoiseStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20 + 2 * kNoiseStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // Noise tiles whose load has been issued.  The two warpgroups take noise tiles from one ring and run out of step;
-  // a warpgroup first waits here until its tile's barrier phase has been armed, so that it cannot mistake the
-  // completed phase of the stage's previous tile for its own.
-  volatile int* noise_issued = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -155,12 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       mbar_init(&pv_done[i], 1);
       mbar_init(&o_free[i], 4);
     }
-    for (int i = 0; i < kNoiseStages; ++i) {
-      mbar_init(&n_full[i], 1);
-      mbar_init(&n_empty[i], 4);
-    }
     *abort_flag = 0;
-    *noise_issued = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -177,7 +152,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const AbortCtx ctx{p.err, abort_flag};
-  constexpr int kSCols = 128;  // tensor-memory columns reserved per S tile (BKV of them used)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -194,10 +168,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           if ((t == 0 ? it.nt[0] : it.nt[1]) == 0) continue;
           if (loads > 0 && !mbar_wait(&q_empty[t], (loads - 1) & 1, ctx, 400)) { ok = false; break; }
           if (lane == 0) {
-            mbar_arrive_expect_tx(&q_full[t], L::kQTile);
+            mbar_arrive_expect_tx(&q_full[t], L::kTile);
 #pragma unroll
             for (int dc = 0; dc < D / 64; ++dc)
-              tma_load_3d(smem + L::kQOff + t * L::kQTile + dc * (BQ * 128), &p.map_q, &q_full[t], dc * 64, it.q0 + t * BQ,
+              tma_load_3d(smem + L::kQOff + t * L::kTile + dc * (BQ * 128), &p.map_q, &q_full[t], dc * 64, it.q0 + t * BQ,
                           it.b * p.Hq + it.hq);
           }
           __syncwarp();
@@ -215,8 +189,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         uint64_t* empty = is_v ? &v_empty[st] : &k_empty[st];
         if (!mbar_wait(empty, ph ^ 1, ctx, is_v ? 402 : 401)) { ok = false; break; }
         if (lane == 0) {
-          mbar_arrive_expect_tx(full, L::kKVTile);
-          uint8_t* dst = smem + (is_v ? L::kVOff : L::kKOff) + st * L::kKVTile;
+          mbar_arrive_expect_tx(full, L::kTile);
+          uint8_t* dst = smem + (is_v ? L::kVOff : L::kKOff) + st * L::kTile;
 #pragma unroll
           for (int dc = 0; dc < D / 64; ++dc)
             tma_load_3d(dst + dc * (BKV * 128), is_v ? &p.map_v : &p.map_k, full, dc * 64, (it.j_begin + j) * BKV,
@@ -225,33 +199,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         __syncwarp();
       }
       ring += static_cast<uint32_t>(it.nt_max);
-    }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------ TMA producer of the noise tiles
-    // ring order: per item, per key tile j, query tile 0 then 1 (where the tile still has keys at j)
-    if (NOISE) {
-      uint32_t n = 0;
-      bool ok = true;
-      for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
-        const Item it = decode_item(p, i);
-        for (int j = 0; ok && j < it.nt_max; ++j) {
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (j >= (t == 0 ? it.nt[0] : it.nt[1])) continue;
-            const uint32_t st = n % kNoiseStages;
-            if (!mbar_wait(&n_empty[st], ((n / kNoiseStages) & 1) ^ 1, ctx, 412)) { ok = false; break; }
-            if (lane == 0) {
-              mbar_arrive_expect_tx(&n_full[st], L::kNoiseTile);
-              tma_load_3d(smem + L::kNoiseOff + st * L::kNoiseTile, &p.map_noise, &n_full[st], (it.j_begin + j) * BKV, it.q0 + t * BQ,
-                          it.b * p.Hq + it.hq);
-              __threadfence_block();  // the armed barrier phase is visible before the count
-              *noise_issued = static_cast<int>(n + 1);
-            }
-            __syncwarp();
-            ++n;
-          }
-        }
-      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -268,21 +215,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     bool ok = true;
 
     auto issue_s = [&](int t) {  // S_t = Q_t K^T with the K tile at ring position kpos
-      const uint64_t qd = make_smem_desc(q_base + t * L::kQTile, 16, 1024);
-      const uint64_t kd = make_smem_desc(k_base + (kpos & 1) * L::kKVTile, 16, 1024);
+      const uint64_t qd = make_smem_desc(q_base + t * L::kTile, 16, 1024);
+      const uint64_t kd = make_smem_desc(k_base + (kpos & 1) * L::kTile, 16, 1024);
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {  // start-address field: 64-column chunk (rows x 128 B each), 32 B per 16 columns
-        const uint64_t qoff = static_cast<uint64_t>(((kk >> 2) * (BQ * 128) + (kk & 3) * 32) >> 4);
-        const uint64_t koff = static_cast<uint64_t>(((kk >> 2) * (BKV * 128) + (kk & 3) * 32) >> 4);
-        umma_ss_warp(tmem_base + t * kSCols, qd + qoff, kd + koff, idesc_s, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4);  // start-address field
+        umma_ss_warp(tmem_base + t * BKV, qd + off, kd + off, idesc_s, kk > 0 ? 1u : 0u);
       }
       umma_commit_warp(&s_full[t]);
     };
     auto issue_pv = [&](int t, bool accumulate) {  // O_t (+)= P_t V, P_t read from tensor memory, V at ring position vpos
-      const uint64_t vd = make_smem_desc(v_base + (vpos & 1) * L::kKVTile, BKV * 128, 1024);
+      const uint64_t vd = make_smem_desc(v_base + (vpos & 1) * L::kTile, BKV * 128, 1024);
 #pragma unroll
       for (int kk = 0; kk < BKV / 16; ++kk)
-        umma_ts_warp(tmem_base + 2 * kSCols + t * D, tmem_base + t * kSCols + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
+        umma_ts_warp(tmem_base + 2 * BKV + t * D, tmem_base + t * BKV + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
                      (accumulate || kk > 0) ? 1u : 0u);
       umma_commit_warp(&pv_done[t]);
     };
@@ -361,34 +307,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       }
       cur = nxt;
     }
-  } else if (warp >= 4) {
+  } else {
     // ------------------------------------------------------------ softmax warps: a thread owns a query row
-    const int t = (warp - 4) >> 2;  // query tile
+    const int t = (warp - 2) >> 2;  // query tile
     const int quad = warp & 3;      // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
     const int r_in = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t tmem_s = tmem_base + t * kSCols + lane_sel;
-    const uint32_t tmem_o = tmem_base + 2 * kSCols + t * D + lane_sel;
+    const uint32_t tmem_s = tmem_base + t * BKV + lane_sel;
+    const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
     uint32_t s_count = 0;  // S tiles consumed so far by this query tile, over all items
-    uint32_t n_base = 0;   // noise tiles of all earlier items (both query tiles)
-    const float st_scale = p.scale_log2 * p.inv_tau;  // (scale*s + noise)/tau in the log2 domain
-    const float nscale = kLog2e * p.inv_tau;
     bool ok = true;
 
     for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
-      int my_nt, k_first, key_limit, n_min = 0;
-      uint32_t n_item = 0;
+      int my_nt, k_first, key_limit;
       {  // only what the key loop needs stays live through it; the item is decoded again for the output addresses
         const Item it = decode_item(p, i);
         my_nt = t == 0 ? it.nt[0] : it.nt[1];
-        n_min = min(it.nt[0], it.nt[1]);
-        n_item = static_cast<uint32_t>(it.nt[0] + it.nt[1]);
         k_first = it.j_begin * BKV;
         const int qi = it.q0 + t * BQ + r_in;
         key_limit = p.causal ? min(p.past + qi, p.kv_len - 1) : p.kv_len - 1;
       }
       float m_use = -INFINITY, l = 0.f;
-      float mt = -INFINITY, lt = 0.f;  // KeyFormer statistic
 
       for (int j = 0; j < my_nt; ++j, ++s_count) {
         const int k0 = k_first + j * BKV;
@@ -413,57 +352,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           mx3 = max3(mx3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
         }
         const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        if (NOISE) {
-          // log-sum-exp of x = (scale*s + noise)/tau in the log2 domain in one sweep over the noise row.  The exponent
-          // reference mt only has to keep exp2(x - mt) inside fp32 range: it starts at the noise-free maximum of the
-          // row's first tile and is moved, after a sweep, when the row's maximum ran more than 2^60 ahead of it.
-          const uint32_t pos = n_base + static_cast<uint32_t>(j < n_min ? 2 * j + t : 2 * n_min + (j - n_min));
-          const uint32_t stg = pos % kNoiseStages;
-          bool armed = *noise_issued > static_cast<int>(pos);
-          if (!armed) {
-            const long long t0 = clock64();
-            while (!(armed = *noise_issued > static_cast<int>(pos))) {
-              if (*ctx.flag) break;
-              if (clock64() - t0 > kWaitLimitCycles) {
-                *ctx.flag = 1;
-                atomicCAS(ctx.gerr, 0, 413);
-                break;
-              }
-            }
-          }
-          if (!armed) { ok = false; break; }
-          __threadfence_block();
-          if (!mbar_wait(&n_full[stg], (pos / kNoiseStages) & 1, ctx, 414)) { ok = false; break; }
-          // row r_in of the swizzled tile: 16-byte unit u lands at u ^ (row & 7)
-          const uint8_t* n_row = smem + L::kNoiseOff + stg * L::kNoiseTile + r_in * 128;
-          if (mt == -INFINITY && rowmax > -INFINITY) mt = rowmax * st_scale;
-          const float neg_ref = (mt == -INFINITY) ? 0.f : -mt;
-          const float2 ss2 = make_float2(st_scale, st_scale), ns2 = make_float2(nscale, nscale), nr2 = make_float2(neg_ref, neg_ref);
-          float tmax0 = -INFINITY, tmax1 = -INFINITY;
-          float2 ta0 = make_float2(0.f, 0.f), ta1 = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int u = 0; u < BKV / 8; ++u) {
-            const uint4 q4 = *reinterpret_cast<const uint4*>(n_row + ((u ^ (r_in & 7)) << 4));
-            const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int c = u * 8 + e * 2;
-              const float2 x = __ffma2_rn(Pack2<T>::unpack(w[e]), ns2,
-                                          __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), ss2, nr2));  // -inf stays -inf
-              if (e & 1) tmax1 = max3(tmax1, x.x, x.y); else tmax0 = max3(tmax0, x.x, x.y);
-              const float2 ex = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-              if (e & 1) ta1 = __fadd2_rn(ta1, ex); else ta0 = __fadd2_rn(ta0, ex);
-            }
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&n_empty[stg]);  // the noise row is in registers
-          lt += (ta0.x + ta0.y) + (ta1.x + ta1.y);
-          const float tmax = fmaxf(tmax0, tmax1);
-          if (tmax > 60.f) {  // move the reference up to this row maximum
-            lt *= fast_exp2(-tmax);
-            mt += tmax;
-          }
-        }
         const float m_new = fmaxf(m_use, rowmax * p.scale_log2);
         const bool grow = m_new > m_use + kRescaleThreshold;  // true on the first tile (m_use = -inf)
         float alpha = 1.f;
@@ -569,12 +457,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           uint4* d = reinterpret_cast<uint4*>(orow);
 #pragma unroll
           for (int e = 0; e < D / 8; ++e) d[e] = make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]);
-          const long long ridx = (static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi;
-          if (p.lse2 != nullptr) p.lse2[ridx] = m_use + log2f(l);
-          if (NOISE && p.lse2_perturbed != nullptr) p.lse2_perturbed[ridx] = mt + log2f(lt);
+          if (p.lse2 != nullptr) p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
         }
       }
-      n_base += n_item;
     }
   }
 
@@ -619,25 +504,18 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   }
 }
 
-template <typename T, int D, int BKV, bool NOISE>
-int launch_variant(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
-  using L = Smem2<D, BKV, NOISE>;
+template <typename T, int D>
+int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
   static bool attr_set[32] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(attn_fwd2_kernel<T, D, BKV, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_fwd2_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<D>::kTotal) != cudaSuccess)
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  attn_fwd2_kernel<T, D, BKV, NOISE><<<grid, kThreads, L::kTotal, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
-}
-
-template <typename T, int D>
-int launch_one(const Attn2Params& p, bool noise, dim3 grid, cudaStream_t stream) {
-  const int status = noise ? launch_variant<T, D, 64, true>(p, grid, stream) : launch_variant<T, D, 128, false>(p, grid, stream);
-  if (status != TB200_OK) return status;
+  attn_fwd2_kernel<T, D><<<grid, kThreads, Smem2<D>::kTotal, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
   if (p.kv_splits > 1) {
     const long long rows = static_cast<long long>(p.B) * p.Hq * p.S;
     long long blocks = (rows * 32 + 255) / 256;
@@ -655,7 +533,7 @@ int launch_one(const Attn2Params& p, bool noise, dim3 grid, cudaStream_t stream)
 // several CTAs per block so that the SMs are filled; 1 = no split.
 int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms) {
   const long long ctas = static_cast<long long>((S + 2 * BQ - 1) / (2 * BQ)) * Hq * B;
-  const int tiles = (kv_len + 127) / 128;
+  const int tiles = (kv_len + BKV - 1) / BKV;
   if (ctas * 2 > num_sms || tiles < 4) return 1;
   int s = static_cast<int>(num_sms / ctas);
   if (s > tiles / 2) s = tiles / 2;
@@ -663,8 +541,7 @@ int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms) {
   return s < 2 ? 1 : s;
 }
 
-// Same contract as launch_attn_fwd; arguments are validated by the caller.  With a noise tensor (KeyFormer) its rows
-// must be 16-byte aligned (kv_len a multiple of 8) and the key range is not split.
+// Same contract as launch_attn_fwd without the KeyFormer statistic; arguments are validated by the caller.
 int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   int status = TB200_OK;
   DeviceState* st = device_state(&status);
@@ -675,11 +552,7 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * kLog2e;
   p.o2 = a.o2;
   p.lse2 = a.lse2;
-  const bool noise = a.noise != nullptr;
-  p.bkv = noise ? 64 : 128;
-  p.inv_tau = 1.f / a.tau;
-  p.lse2_perturbed = a.lse2_perturbed;
-  p.kv_splits = (!noise && a.kv_splits > 1 && a.part_o != nullptr && a.part_ml != nullptr) ? a.kv_splits : 1;
+  p.kv_splits = (a.kv_splits > 1 && a.part_o != nullptr && a.part_ml != nullptr) ? a.kv_splits : 1;
   p.part_o = a.part_o;
   p.part_ml = a.part_ml;
   p.err = st->err_word;
@@ -693,16 +566,9 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(p.kv_len), static_cast<uint64_t>(a.B) * a.Hkv};
     const uint64_t strides[2] = {D * 2, static_cast<uint64_t>(a.cache_len) * D * 2};
-    const uint32_t box[3] = {64, static_cast<uint32_t>(p.bkv), 1};
+    const uint32_t box[3] = {64, BKV, 1};
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
     if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
-  }
-  if (noise) {
-    if ((p.kv_len & 7) != 0) return TB200_ERR_INVALID;
-    const uint64_t dims[3] = {static_cast<uint64_t>(p.kv_len), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
-    const uint64_t strides[2] = {static_cast<uint64_t>(p.kv_len) * 2, static_cast<uint64_t>(a.S) * p.kv_len * 2};
-    const uint32_t box[3] = {64, BQ, 1};
-    if ((status = make_tensor_map(&p.map_noise, a.noise, 3, dims, strides, box)) != TB200_OK) return status;
   }
   p.n_blocks = (a.S + 2 * BQ - 1) / (2 * BQ);
   const long long items = static_cast<long long>(p.n_blocks) * p.kv_splits * a.Hq * a.B;
@@ -710,9 +576,9 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.n_items = static_cast<int>(items);
   const dim3 grid(static_cast<unsigned>(p.n_items < st->num_sms ? p.n_items : st->num_sms), 1, 1);  // persistent: one CTA per SM
   if (a.dtype == TB200_BF16) {
-    return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, noise, grid, stream) : launch_one<__nv_bfloat16, 64>(p, noise, grid, stream);
+    return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
   }
-  return a.D == 128 ? launch_one<__half, 128>(p, noise, grid, stream) : launch_one<__half, 64>(p, noise, grid, stream);
+  return a.D == 128 ? launch_one<__half, 128>(p, grid, stream) : launch_one<__half, 64>(p, grid, stream);
 }
 
 }  // namespace tb200

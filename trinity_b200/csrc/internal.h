@@ -135,6 +135,8 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream);
 // attn2.cu: two query tiles per CTA; chosen by launch_attn_fwd when there is no noise tensor
 int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream);
 int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms);
+// attn_kf.cu: the same kernel with the KeyFormer statistic (noise tiles by TMA; kv_len a multiple of 8)
+int launch_attn_fwd_keyformer(const AttnLaunch& a, cudaStream_t stream);
 
 // ---------------------------------------------------------------- score.cu
 struct ScoreLaunch {
