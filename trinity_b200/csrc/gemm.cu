@@ -7,7 +7,7 @@
 //               (two 256-column accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
 //   warps 2-5   epilogue: tcgen05.ld (thread = output row, 32 columns at a time) -> fused epilogue -> global
 // No cluster launch and no multicast: every CTA fetches its own operands; reuse comes from L2, for which
-// the tile order walks groups of kGroupM row-tiles across all column tiles.
+// the tile order walks groups of row-tiles across all column tiles.
 //
 // The four B boxes of a stage may come from different weight tensors:
 //   GEMM_STORE / GEMM_PARTIAL  one source, 256 consecutive columns
@@ -36,7 +36,7 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + slack to align the ring to 1 KiB
 constexpr int kThreads = 192;
-constexpr int kGroupM = 32;
+constexpr int kGroupRows = 4096;  // rows of A whose tiles are walked across all column tiles before moving down
 constexpr int kTmemCols = 512;
 // CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 256 tile.  Each CTA stages its own 128 A
 // rows and HALF of the B columns (two boxes), so a stage is 32 KiB and six stages fit where four did.
@@ -53,6 +53,7 @@ struct GemmParams {
   int src_tile0[4];   // first column-tile of each source (prefix sums); [n_src] = number of column tiles
   int tile_n;         // output columns per tile (256, or 128 for SwiGLU)
   int m_tiles, n_tiles, total_units;
+  int group_m;        // row-tiles per L2 group
   int* err;
   // epilogue
   const float* row_scale;
@@ -89,7 +90,9 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u, int rank
   Unit r;
   const int tile = u / p.split_k;
   r.split = u - tile * p.split_k;
-  // groups of kGroupM row-tiles walk all column tiles before moving down: A and B stay L2-resident
+  // Groups of p.group_m row-tiles walk all column tiles before moving down: the group's slice of A stays in L2
+  // while the weights stream by (see launch_gemm for its size).
+  const int kGroupM = p.group_m;
   const int per_group = kGroupM * p.n_tiles;
   const int g = tile / per_group;
   const int rem = tile - g * per_group;
@@ -631,6 +634,11 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.n_tiles = tiles;
   const bool pair = use_pair(g.M, static_cast<long long>((g.M + 2 * BM - 1) / (2 * BM)) * tiles * p.split_k, st->num_sms);
   p.m_tiles = pair ? (g.M + 2 * BM - 1) / (2 * BM) : (g.M + BM - 1) / BM;
+  // 4096 rows of A per group.  At K = 4096 that slice is 32 MiB and stays in the half of L2 next to each die while
+  // the weights stream by (with 8192 rows the Llama QKV projection read 908 MB from DRAM, with 4096 rows 430 MB);
+  // a sweep of 2..32 row-tiles on the K = 14336 and K = 18176 projections of the FFNs also had its best times here.
+  p.group_m = kGroupRows / (pair ? 2 * BM : BM);
+  if (p.group_m > p.m_tiles) p.group_m = p.m_tiles;
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.split_k;
   if (units > 0x7fffffffLL) return TB200_ERR_INVALID;
   p.total_units = static_cast<int>(units);
@@ -783,6 +791,7 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   p.K = K;
   p.k_blocks = (K + BK - 1) / BK;
   p.m_tiles = (M + BM - 1) / BM;
+  p.group_m = p.m_tiles;  // decode-size M: one group
   p.n_tiles = n_src * ((N + BN - 1) / BN);
   int split = a->split_k;
   if (split == 0) {  // as many slices as fill the SMs once, at least four K blocks each
