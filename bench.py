@@ -49,7 +49,7 @@ WORKLOADS = {
 DEFAULT = "llama3_8b_vanilla_prefill_b8_s2048"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from an ncu capture of this very
 # command at full size (profiles/traffic_llama_b8_s2048.md); null where no capture has been taken.
-NCU_TRAFFIC = {"llama3_8b_vanilla_prefill_b8_s2048": 667_890_176}
+NCU_TRAFFIC = {"llama3_8b_vanilla_prefill_b8_s2048": 613_224_192}
 
 
 def block_flops(w, batch=None):
