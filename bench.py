@@ -36,6 +36,10 @@ WORKLOADS = {
     "llama3_8b_qknorm_prefill_b8_s2048": dict(B=8, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="qknorm"),
     "llama3_8b_prenorm_b8_s4096": dict(B=8, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="prenorm"),
     "falcon_7b_vanilla_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="vanilla"),
+    "falcon_7b_prenorm_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="prenorm"),
+    "falcon_7b_qknorm_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="qknorm"),
+    "falcon_7b_roco_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="roco", topk=1024),
+    "falcon_7b_keyformer_b16_s2048": dict(B=16, S=2048, N=4544, Hq=71, Hkv=1, D=64, variant="keyformer", topk=1024),
     "llama3_8b_roco_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="roco", topk=1024),
     "llama3_8b_keyformer_b4_s4096": dict(B=4, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="keyformer", topk=1024),
     "llama3_8b_keyformer_b1_s4096": dict(B=1, S=4096, N=4096, Hq=32, Hkv=8, D=128, variant="keyformer", topk=1024),   # profiling size
