@@ -8,15 +8,19 @@
 // core, S^T = K_tile Q_i^T, so that a TMEM lane is a key and its columns are the queries: the sum over
 // queries is then a thread-local loop -- no atomics, run-to-run identical.
 //   warp 0      TMA: the K tile once, then the Q tiles that can see it (two-deep ring)
-//   warp 1      MMA: S^T into four 128-column TMEM buffers
+//   warp 1      MMA: S^T into 128-column TMEM buffers (one per group for RoCo, two for KeyFormer)
 //   warp 2      TMA (KeyFormer): the noise tiles through a ring of their own, three or four deep -- the pass
 //               streams the noise tensor, so enough of it must be in flight, and its waits must not hold up Q
-//   warps 4-19  reduction, in G groups; group g takes query tiles g, g+G, ...  The groups run out of step, so while
-//               one waits for its next S^T tile, copies row statistics or loads from tensor memory, the others
-//               keep the special-function unit busy (with all warps in step those phases were measured to cost
-//               as much as the exponentials).  RoCo: G = 4 groups of four warps, thread = key.  KeyFormer: G = 2
-//               groups of eight warps, thread = (key, half of the tile's queries) -- a group holds a noise stage
-//               while it works on a tile, and with only three stages the tile has to be finished quickly.
+//   warps 4-..  reduction, in two groups that take alternate query tiles.  The groups run out of step, so while
+//               one waits for its next S^T tile, copies row statistics or loads from tensor memory, the other
+//               keeps the special-function unit busy (with all warps in step those phases were measured to cost
+//               as much as the exponentials).
+//               RoCo: two groups of four warps, thread = key, and TWO CTAs per SM (384 threads, 104 KB of shared
+//               memory, 256 tensor-memory columns each), so that the start and the end of a CTA -- a tenth of the
+//               time at S = 4096, a third at S = 2048 -- overlap the other CTA's tiles.
+//               KeyFormer: two groups of eight warps, thread = (key, half of the tile's queries), one CTA per SM:
+//               the noise ring takes the shared memory, and a group holds a noise stage while it works on a
+//               tile, so with only three stages the tile has to be finished quickly.
 //               The partial sums are added in a fixed order at the end.
 #include <math.h>
 #include <string.h>
@@ -30,23 +34,33 @@ namespace {
 
 constexpr int BK_ = 128;  // keys per CTA
 constexpr int BQ_ = 128;  // queries per step
-constexpr int kReducers = 512;
-constexpr int kThreads = 128 + kReducers;  // warps 0..3: K/Q producer, MMA issuer, noise producer, idle
-constexpr int kTmemCols = 512;  // four S^T buffers
+constexpr int G = 2;  // reducer groups
+template <bool NOISE> struct ScoreCfg {
+  static constexpr int kReducerWarps = NOISE ? 16 : 8;
+  static constexpr int kThreads = 128 + 32 * kReducerWarps;  // warps 0..3: K/Q producer, MMA issuer, noise producer, idle
+  static constexpr int kCtasPerSm = NOISE ? 1 : 2;
+  static constexpr int kGroupWarps = kReducerWarps / G;
+  static constexpr int kParts = kGroupWarps / 4;      // warps of a group that share a quarter of the keys and split the queries
+  static constexpr int kChunks = 4 / kParts;          // 32-query chunks each warp sums per tile
+  static constexpr int kSBuffers = NOISE ? 4 : 2;     // S^T buffers in tensor memory
+  static constexpr int kTmemCols = kSBuffers * 128;
+  static constexpr int kLseBuffers = 3 * kSBuffers;
+};
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D, bool NOISE> struct ScoreSmem {
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kNoiseBytes = 128 * 128 * 2;              // [2 chunks of 64 keys][128 queries][128 B], swizzled
-  static constexpr int kNoiseStages = (D == 128) ? 3 : 4;        // what fits beside K and the Q ring
-  static constexpr int kQStages = (NOISE && D == 128) ? 2 : 4;
+  static constexpr int kNoiseStages = 3;                         // what fits beside K and the Q ring at D = 128
+  static constexpr int kQStages = (D == 128) ? 2 : 4;
   static constexpr int kKOff = 0;
   static constexpr int kQOff = kTileBytes;
   static constexpr int kNoiseOff = kQOff + kQStages * kTileBytes;  // ring (KeyFormer only)
   static constexpr int kLseOff = kNoiseOff + (NOISE ? kNoiseStages * kNoiseBytes : 0);  // [8 buffers][2 statistics][128] fp32
-  static constexpr int kRedOff = kLseOff + 8 * 2 * 128 * 4;      // [3 sums][4 partial sums][128 keys] fp32
+  static constexpr int kRedOff = kLseOff + ScoreCfg<NOISE>::kLseBuffers * 2 * 128 * 4;  // [3 sums][4 partial sums][128 keys] fp32
   static constexpr int kBarOff = kRedOff + 3 * 4 * 128 * 4;
   static constexpr int kTotal = kBarOff + 512 + 1024;
+  static_assert(kTotal <= 232448 / ScoreCfg<NOISE>::kCtasPerSm - 1024 * (ScoreCfg<NOISE>::kCtasPerSm - 1), "shared memory of an SM");
 };
 
 struct ScoreParams {
@@ -66,14 +80,15 @@ struct ScoreParams {
 };
 
 template <typename T, int D, bool NOISE>
-__global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constant__ ScoreParams p) {
+__global__ void __launch_bounds__(ScoreCfg<NOISE>::kThreads, ScoreCfg<NOISE>::kCtasPerSm)
+score_kernel(const __grid_constant__ ScoreParams p) {
   using L = ScoreSmem<D, NOISE>;
+  using C = ScoreCfg<NOISE>;
+  constexpr int kGroupWarps = C::kGroupWarps, kParts = C::kParts, kChunks = C::kChunks;
+  constexpr int SB = C::kSBuffers, LB = C::kLseBuffers;
   constexpr int kNoiseStages = L::kNoiseStages;
   constexpr int QS = L::kQStages;
   constexpr int kPrefetch = 6;  // tiles asked into L2 ahead of the ring
-  constexpr int G = NOISE ? 2 : 4;        // reducer groups
-  constexpr int kGroupWarps = 16 / G;
-  constexpr int kParts = 4 / G;           // warps of a group that share a quarter of the keys and split the queries
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -84,8 +99,8 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
   uint64_t* s_empty = bars + 13; // [4]
   uint64_t* n_full = bars + 17;  // [kNoiseStages] noise tiles
   uint64_t* n_empty = bars + 17 + kNoiseStages;
-  uint64_t* lse_ready = bars + 17 + 2 * kNoiseStages;  // [8] the row statistics of a query tile are staged
-  uint64_t* red_done = lse_ready + 8;                 // every reducer has published its partial sums
+  uint64_t* lse_ready = bars + 17 + 2 * kNoiseStages;  // [LB] the row statistics of a query tile are staged
+  uint64_t* red_done = lse_ready + 12;                // every reducer has published its partial sums
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // Noise tiles whose load has been issued.  The reducer groups run out of step and a ring stage serves tiles of
@@ -113,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < SB; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], kGroupWarps);  // one arrival per warp of the group that owns the tile
     }
@@ -121,14 +136,14 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
       mbar_init(&n_full[i], 1);
       mbar_init(&n_empty[i], kGroupWarps);
     }
-    for (int i = 0; i < 8; ++i) mbar_init(&lse_ready[i], kGroupWarps);  // the warps of the owning group
-    mbar_init(red_done, kReducers / 32);
+    for (int i = 0; i < LB; ++i) mbar_init(&lse_ready[i], kGroupWarps);  // the warps of the owning group
+    mbar_init(red_done, C::kReducerWarps);
     *abort_flag = 0;
     *noise_issued = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -193,9 +208,9 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
     const uint32_t k_s = smem_u32(smem + L::kKOff);
     bool ok = mbar_wait(k_full, 0, ctx, 302);
     for (int i = 0; ok && i < nt; ++i) {
-      const int st = i & 3;
+      const int st = i % SB;
       const int qs = i % QS;
-      const uint32_t ph = (i >> 2) & 1;
+      const uint32_t ph = (i / SB) & 1;
       if (!mbar_wait(&q_full[qs], (i / QS) & 1, ctx, 303)) break;
       if (!mbar_wait(&s_empty[st], ph ^ 1, ctx, 304)) break;
       tc_fence_after();
@@ -227,9 +242,10 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
     // The first 128 threads of a group stage lse2 of the queries of the group's tile, the last 128 (the same ones when
     // the group has four warps) the perturbed statistic of KeyFormer; values are fetched three of the group's tiles
     // ahead: a tile takes about as long as one trip to L2.  +inf for rows past the end makes their probability 0.
-    // Buffer i & 7 is written again for tile i+8 by the same group.  A warp that is there has been handed the S^T
-    // buffer of tile i+4, which is given out only after every warp of the group released tile i, i.e. has the
-    // tile's statistics in registers: no warp runs more than one phase of a buffer's barrier ahead of another.
+    // There are three times as many statistics buffers as S^T buffers; buffer i % LB is written again for tile i + LB
+    // by the same group.  A warp that is there has been handed the S^T buffer of tile i + 2 LB / 3, which is given out
+    // only after every warp of the group released tile i + LB / 3, i.e. is done with tile i (whose statistics are read
+    // while it is summed): no warp runs more than one phase of a buffer's barrier ahead of another.
     const bool stage_a = part == 0, stage_b = NOISE && part == kParts - 1;
     auto fetch_stat = [&](const float* src, int tile) -> float {
       const int qi = (first_tile + tile) * BQ_ + r_in;
@@ -247,8 +263,8 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
       sb2 = fetch_stat(p.lse2t, grp + 2 * G);
     }
     for (int i = grp; i < nt; i += G) {
-      const int st = i & 3;
-      const int lb = i & 7;
+      const int st = i % SB;
+      const int lb = i % LB;
       const int q0 = (first_tile + i) * BQ_;
       if (stage_a) lse_s[(lb * 2 + 0) * 128 + r_in] = sa0;
       if (stage_b) lse_s[(lb * 2 + 1) * 128 + r_in] = sb0;
@@ -264,9 +280,9 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
         sb1 = sb2;
         sb2 = fetch_stat(p.lse2t, i + 3 * G);
       }
-      if (!mbar_wait(&s_full[st], (i >> 2) & 1, ctx, 305)) break;
+      if (!mbar_wait(&s_full[st], (i / SB) & 1, ctx, 305)) break;
       tc_fence_after();
-      if (!mbar_wait(&lse_ready[lb], (i >> 3) & 1, ctx, 308)) break;
+      if (!mbar_wait(&lse_ready[lb], (i / LB) & 1, ctx, 308)) break;
       const int ns = i % kNoiseStages;
       if (NOISE && p.noise_tma) {
         bool armed = *noise_issued > i;
@@ -286,24 +302,21 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
         if (!mbar_wait(&n_full[ns], (i / kNoiseStages) & 1, ctx, 307)) break;
       }
 #pragma unroll 1
-      for (int ch = 0; ch < G; ++ch) {  // this warp's query columns, 32 at a time
-        const int cb = (part * G + ch) * 32;
+      for (int ch = 0; ch < kChunks; ++ch) {  // this warp's query columns, 32 at a time
+        const int cb = (part * kChunks + ch) * 32;
         uint32_t s[32];
         tmem_ld_x32(tmem_base + st * BQ_ + lane_sel + cb, s);
         // this key's column of the swizzled noise tile: element (query c, key r_in)
         const uint8_t* n_col = smem + L::kNoiseOff + ns * L::kNoiseBytes + (r_in >> 6) * (128 * 128) + (cb) * 128 + (r_in & 7) * 2;
         const int n_unit = (r_in & 63) >> 3;
-        float4 lq4[8];  // the statistic of these 32 queries
-        {
-          const float4* src = reinterpret_cast<const float4*>(lse_s + (lb * 2 + (NOISE ? 1 : 0)) * 128 + cb);
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) lq4[e4] = src[e4];
-        }
+        // the statistic of these 32 queries, read four at a time where it is used (the buffer stays valid until the
+        // group's third tile from here, see above)
+        const float4* lq4 = reinterpret_cast<const float4*>(lse_s + (lb * 2 + (NOISE ? 1 : 0)) * 128 + cb);
         // query column c of the tile is visible to this key iff kj <= past + q0 + c; only tiles on the diagonal mask
         const int c_min = (p.causal ? kj - p.past - q0 : 0) - cb;
         const bool mask_tile = !key_ok || c_min > 0;
         tmem_wait_ld();
-        if (ch == G - 1) {  // the last of this warp's S^T columns is in registers: the buffer may be overwritten
+        if (ch == kChunks - 1) {  // the last of this warp's S^T columns is in registers: the buffer may be overwritten
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_empty[st]);
@@ -382,8 +395,11 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
       float t[3];
 #pragma unroll
       for (int w = 0; w < 3; ++w)
-        t[w] = ((red_s[(w * 4 + 0) * 128 + r_in] + red_s[(w * 4 + 1) * 128 + r_in]) + red_s[(w * 4 + 2) * 128 + r_in]) +
-               red_s[(w * 4 + 3) * 128 + r_in];
+      {
+        t[w] = red_s[(w * 4 + 0) * 128 + r_in];
+#pragma unroll
+        for (int slot = 1; slot < G * kParts; ++slot) t[w] += red_s[(w * 4 + slot) * 128 + r_in];
+      }
       if (p.sum_p) p.sum_p[o] = t[0];
       if (p.sum_p2) p.sum_p2[o] = t[1];
       if (NOISE && p.sum_pt) p.sum_pt[o] = t[2];
@@ -394,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) score_kernel(const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -408,7 +424,7 @@ int launch_one(const ScoreParams& p, dim3 grid, cudaStream_t stream) {
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  score_kernel<T, D, NOISE><<<grid, kThreads, ScoreSmem<D, NOISE>::kTotal, stream>>>(p);
+  score_kernel<T, D, NOISE><<<grid, ScoreCfg<NOISE>::kThreads, ScoreSmem<D, NOISE>::kTotal, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
