@@ -265,3 +265,35 @@ def test_full_size_prefill_properties():
     ops.attn_forward(g["X"][1:].contiguous(), g["WQ"], g["WK"], g["WV"], kc[1:].clone(), vc[1:].clone(), o2b, past=0,
                      head_dim=D, flags=C, sm_scale=D ** -0.5)
     assert torch.equal(o2b[0], o2[1])
+
+
+def test_full_size_keyformer_properties():
+    """Llama-3-8B KeyFormer, one sequence of the benchmark's batch at seq 2048 (256 work items for 148 persistent
+    CTAs, a 268 MB noise tensor): everything against the oracle, plus the property that the per-key scores of a head add
+    up to the number of queries (every perturbed softmax row sums to one)."""
+    B, S, N, Hq, Hkv, D = 1, 2048, 4096, 32, 8, 128
+    got, ref = attention_case(B, S, N, Hq, Hkv, D, 0, C | KF, topk=1024, tau=1.0, seed=7)
+    close(got["O2"], ref["O2"], msg="O2")
+    close(got["C_out"], ref["C_out"], msg="C_out")
+    close(got["C_out"].sum(-1), torch.full((B, Hq), float(S)), rtol=1e-3, atol=0.5, msg="scores add up to S")
+    assert torch.equal(got["topk_idx"].cpu(), orc.stable_topk(got["C_out"].float().cpu(), 1024))
+
+
+@pytest.mark.parametrize("flags", [C | RC, C | KF, C | Pn | Q])
+def test_falcon_shapes_multi_item(flags):
+    """Falcon-7B geometry (hidden 4544, MQA 71/1, head_dim 64) at batch 2, seq 1024: 568 work items, so every
+    persistent CTA walks several items of different lengths; against the oracle."""
+    B, S, N, Hq, Hkv, D = 2, 1024, 4544, 71, 1, 64
+    kw = dict(topk=256) if flags & (RC | KF) else dict(weights=True)
+    got, ref = attention_case(B, S, N, Hq, Hkv, D, 0, flags, seed=11, **kw)
+    close(got["O2"], ref["O2"], msg="O2")
+    close(got["K_new"], ref["K_new"], msg="appended K rows")
+    if flags & RC:
+        close(got["C_out1"], ref["C_out1"], msg="C_out1")
+        close(got["C_out2"], ref["C_out2"], msg="C_out2")
+        close(got["C_out1"].sum(-1), torch.full((B, Hq), float(S)), rtol=1e-3, atol=0.5, msg="column sums add up to S")
+        assert torch.equal(got["topk_idx"].cpu(), orc.stable_topk(got["C_out1"].float().cpu(), 256))
+    if flags & KF:
+        close(got["C_out"], ref["C_out"], msg="C_out")
+        close(got["C_out"].sum(-1), torch.full((B, Hq), float(S)), rtol=1e-3, atol=0.5, msg="scores add up to S")
+        assert torch.equal(got["topk_idx"].cpu(), orc.stable_topk(got["C_out"].float().cpu(), 256))
