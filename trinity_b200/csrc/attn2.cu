@@ -48,11 +48,30 @@ template <int D> struct Smem2 {
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
+// Division by a value fixed for the launch as a multiply and a shift: decoding an item takes four divisions, and as
+// emulated 32-bit divisions they cost each role about a thousand cycles per item.  Valid for n < 2^31.
+struct FastDiv {
+  uint32_t mul, shr, d;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d;
+  uint32_t s = 0;
+  while ((1ull << s) < d) ++s;
+  f.shr = s;
+  f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << s) - d)) / d + 1);
+  return f;
+}
+__device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
+  return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shr);
+}
+
 struct Attn2Params {
   CUtensorMap map_q, map_k, map_v;
   int B, S, Hq, Hkv, past, kv_len, causal;
   int n_blocks;      // blocks of 256 queries
   int n_items;       // n_blocks * kv_splits * Hq * B
+  FastDiv d_per_blk, d_splits, d_hq, d_group;  // B * Hq * kv_splits, kv_splits, Hq, Hq / Hkv
   float scale_log2;
   void* o2;
   float* lse2;
@@ -76,14 +95,13 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
   it.nt[0] = it.nt[1] = it.nt_max = 0;
   it.q0 = it.hq = it.b = it.hkv = it.sp = it.j_begin = 0;
   if (i >= p.n_items) return it;
-  const int per_blk = p.B * p.Hq * p.kv_splits;
-  const int blk = i / per_blk;
-  int rem = i - blk * per_blk;
-  it.sp = rem % p.kv_splits;
-  rem /= p.kv_splits;
-  it.hq = rem % p.Hq;
-  it.b = rem / p.Hq;
-  it.hkv = it.hq / (p.Hq / p.Hkv);
+  const int blk = fdiv(i, p.d_per_blk);
+  int rem = i - blk * static_cast<int>(p.d_per_blk.d);
+  const int r1 = fdiv(rem, p.d_splits);
+  it.sp = rem - r1 * p.kv_splits;
+  it.b = fdiv(r1, p.d_hq);
+  it.hq = r1 - it.b * p.Hq;
+  it.hkv = fdiv(it.hq, p.d_group);
   it.q0 = (p.n_blocks - 1 - blk) * 2 * BQ;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -92,10 +110,12 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
     if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
     it.nt[t] = (q0t < p.S) ? last_key / BKV + 1 : 0;
   }
-  const int per_split = (max(it.nt[0], it.nt[1]) + p.kv_splits - 1) / p.kv_splits;
-  it.j_begin = it.sp * per_split;
+  if (p.kv_splits > 1) {
+    const int per_split = fdiv(max(it.nt[0], it.nt[1]) + p.kv_splits - 1, p.d_splits);
+    it.j_begin = it.sp * per_split;
 #pragma unroll
-  for (int t = 0; t < 2; ++t) it.nt[t] = max(0, min(it.nt[t], it.j_begin + per_split) - it.j_begin);
+    for (int t = 0; t < 2; ++t) it.nt[t] = max(0, min(it.nt[t], it.j_begin + per_split) - it.j_begin);
+  }
   it.nt_max = max(it.nt[0], it.nt[1]);
   return it;
 }
@@ -457,8 +477,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           uint4* d = reinterpret_cast<uint4*>(orow);
 #pragma unroll
           for (int e = 0; e < D / 8; ++e) d[e] = make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]);
-          if (p.lse2 != nullptr) p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
         }
+        if (row_ok && p.lse2 != nullptr) p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
       }
     }
   }
@@ -574,6 +594,10 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(p.n_blocks) * p.kv_splits * a.Hq * a.B;
   if (items > 0x7fffffffLL) return TB200_ERR_INVALID;
   p.n_items = static_cast<int>(items);
+  p.d_per_blk = make_fastdiv(static_cast<uint32_t>(a.B) * a.Hq * p.kv_splits);
+  p.d_splits = make_fastdiv(static_cast<uint32_t>(p.kv_splits));
+  p.d_hq = make_fastdiv(static_cast<uint32_t>(a.Hq));
+  p.d_group = make_fastdiv(static_cast<uint32_t>(a.Hq / a.Hkv));
   const dim3 grid(static_cast<unsigned>(p.n_items < st->num_sms ? p.n_items : st->num_sms), 1, 1);  // persistent: one CTA per SM
   if (a.dtype == TB200_BF16) {
     return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
