@@ -61,6 +61,23 @@ template <int D, int BKV, bool NOISE> struct Smem2 {
   static_assert(!NOISE || BKV == 64, "a noise tile is one 128-byte-wide swizzled block");
 };
 
+// Division by a value fixed for the launch as a multiply and a shift (item decoding; valid for n < 2^31).
+struct FastDiv {
+  uint32_t mul, shr, d;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d;
+  uint32_t s = 0;
+  while ((1ull << s) < d) ++s;
+  f.shr = s;
+  f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << s) - d)) / d + 1);
+  return f;
+}
+__device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
+  return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shr);
+}
+
 struct Attn2Params {
   CUtensorMap map_q, map_k, map_v;
   CUtensorMap map_noise;       // dims {past+S, S, B*Hq}, box {64, 128, 1} (KeyFormer)
@@ -70,6 +87,7 @@ struct Attn2Params {
   int B, S, Hq, Hkv, past, kv_len, causal;
   int n_blocks;      // blocks of 256 queries
   int n_items;       // n_blocks * kv_splits * Hq * B
+  FastDiv d_per_blk, d_hq, d_group;  // B * Hq, Hq, Hq / Hkv
   float scale_log2;
   void* o2;
   float* lse2;
@@ -93,14 +111,12 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
   it.nt[0] = it.nt[1] = it.nt_max = 0;
   it.q0 = it.hq = it.b = it.hkv = it.sp = it.j_begin = 0;
   if (i >= p.n_items) return it;
-  const int per_blk = p.B * p.Hq * p.kv_splits;
-  const int blk = i / per_blk;
-  int rem = i - blk * per_blk;
-  it.sp = rem % p.kv_splits;
-  rem /= p.kv_splits;
-  it.hq = rem % p.Hq;
-  it.b = rem / p.Hq;
-  it.hkv = it.hq / (p.Hq / p.Hkv);
+  const int blk = fdiv(i, p.d_per_blk);  // the key range is never split here (kv_splits = 1)
+  const int rem = i - blk * static_cast<int>(p.d_per_blk.d);
+  it.sp = 0;
+  it.b = fdiv(rem, p.d_hq);
+  it.hq = rem - it.b * p.Hq;
+  it.hkv = fdiv(it.hq, p.d_group);
   it.q0 = (p.n_blocks - 1 - blk) * 2 * BQ;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -109,10 +125,7 @@ __device__ __forceinline__ Item decode_item(const Attn2Params& p, int i) {
     if (p.causal) last_key = min(last_key, p.past + min(q0t + BQ - 1, p.S - 1));
     it.nt[t] = (q0t < p.S) ? last_key / p.bkv + 1 : 0;
   }
-  const int per_split = (max(it.nt[0], it.nt[1]) + p.kv_splits - 1) / p.kv_splits;
-  it.j_begin = it.sp * per_split;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) it.nt[t] = max(0, min(it.nt[t], it.j_begin + per_split) - it.j_begin);
+  it.j_begin = 0;
   it.nt_max = max(it.nt[0], it.nt[1]);
   return it;
 }
@@ -690,6 +703,9 @@ int launch_attn_fwd_keyformer(const AttnLaunch& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(p.n_blocks) * p.kv_splits * a.Hq * a.B;
   if (items > 0x7fffffffLL) return TB200_ERR_INVALID;
   p.n_items = static_cast<int>(items);
+  p.d_per_blk = make_fastdiv(static_cast<uint32_t>(a.B) * a.Hq);
+  p.d_hq = make_fastdiv(static_cast<uint32_t>(a.Hq));
+  p.d_group = make_fastdiv(static_cast<uint32_t>(a.Hq / a.Hkv));
   const dim3 grid(static_cast<unsigned>(p.n_items < st->num_sms ? p.n_items : st->num_sms), 1, 1);  // persistent: one CTA per SM
   if (a.dtype == TB200_BF16) {
     return a.D == 128 ? launch_variant<__nv_bfloat16, 128, 64, true>(p, grid, stream) : launch_variant<__nv_bfloat16, 64, 64, true>(p, grid, stream);
