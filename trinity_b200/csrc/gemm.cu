@@ -54,6 +54,8 @@ struct GemmParams {
   int tile_n;         // output columns per tile (256, or 128 for SwiGLU)
   int m_tiles, n_tiles, total_units;
   int group_m;        // row-tiles per L2 group
+  int kv_merged;      // GEMM_QKV with at most 128 columns each of Wk and Wv: one tile holds both (K in accumulator
+                      // columns [0,128), V in [128,256)) instead of two tiles that are three quarters empty
   int* err;
   // epilogue
   const float* row_scale;
@@ -206,6 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
               const int g = rank * NCH + c;  // box of the pair's 256-column B tile
               int src = t.src, col = t.n0 + 64 * g;
               if (MODE == GEMM_SWIGLU) { src = g >> 1; col = t.n0 + 64 * (g & 1); }
+              if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (g >> 1); col = 64 * (g & 1); }
               tma_load_2d_pair(sb + c * kBChunkBytes, &p.map_b[src], fb, col, kb * BK);
             }
           } else {
@@ -215,6 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             for (int c = 0; c < NCH; ++c) {
               int src = t.src, col = t.n0 + 64 * c;
               if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
+              if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (c >> 1); col = 64 * (c & 1); }
               tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
             }
           }
@@ -351,17 +355,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
       } else {  // GEMM_QKV
         const int D = p.D;
-        const int n_total = p.src_n[t.src];
         const int b = row_ok ? row / p.S : 0;
         const int s_in = row_ok ? row - b * p.S : 0;
-        const int heads_here = BN / D;  // 2 (D=128) or 4 (D=64) heads per tile
-        const bool norm_this = p.qknorm && t.src < 2;
-        const T* nw = static_cast<const T*>(t.src == 0 ? p.q_norm_weight : p.k_norm_weight);
+        const bool merged = p.kv_merged && t.src == 1;   // K in accumulator columns [0,128), V in [128,256)
+        const int heads_all = (merged ? BN / 2 : BN) / D;  // heads per source in this tile
 #pragma unroll 1
-        for (int hh = 0; hh < heads_here; ++hh) {
-          const int col_h = t.n0 + hh * D;
-          if (col_h >= n_total) break;
+        for (int hx = 0; hx < (merged ? 2 : 1) * heads_all; ++hx) {
+          const int part = hx / heads_all, hh_in = hx - part * heads_all;
+          const int psrc = t.src + part;
+          const int n_total = p.src_n[psrc];
+          const bool norm_this = p.qknorm && psrc < 2;
+          const T* nw = static_cast<const T*>(psrc == 0 ? p.q_norm_weight : p.k_norm_weight);
+          const int col_h = (merged ? 0 : t.n0) + hh_in * D;
+          if (col_h >= n_total) continue;
           const int head = col_h / D;
+          const int hh = part * heads_all + hh_in;  // position of the head in the accumulator: column hh * D
           float scale = rs;
           if (norm_this) {  // pass 1: sum of squares over the head's D columns (thread-local: a thread owns a row)
             float ss = 0.f;
@@ -377,10 +385,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             scale = rs * rsqrtf(ss / static_cast<float>(D) + p.qk_eps);
           }
           T* dst;
-          if (t.src == 0) {
+          if (psrc == 0) {
             dst = static_cast<T*>(p.q_out) + ((static_cast<long long>(b) * p.Hq + head) * p.S + s_in) * D;
           } else {
-            T* cache = static_cast<T*>(t.src == 1 ? p.k_cache : p.v_cache);
+            T* cache = static_cast<T*>(psrc == 1 ? p.k_cache : p.v_cache);
             dst = cache + ((static_cast<long long>(b) * p.Hkv + head) * p.cache_len + p.past + s_in) * D;
           }
           for (int c = 0; c < D / 32; ++c) {
@@ -629,6 +637,11 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     if (g.C == nullptr || !aligned16(g.C) || (g.ldc & 7) != 0 || !aligned16(g.residual) || (g.ldr & 7) != 0) return TB200_ERR_INVALID;
   }
   if (g.mode == GEMM_PARTIAL && (g.partial == nullptr || !aligned16(g.partial))) return TB200_ERR_INVALID;
+  if (g.mode == GEMM_QKV && g.N[1] <= BN / 2 && g.N[2] <= BN / 2) {  // MQA / small GQA: K and V share one tile
+    p.kv_merged = 1;
+    tiles = p.src_tile0[1] + 1;
+    p.src_tile0[2] = tiles;  // no tile of its own for Wv
+  }
   for (int s = g.n_src; s < 4; ++s) p.src_tile0[s] = tiles;
   p.src_tile0[g.n_src] = tiles;
   p.n_tiles = tiles;
