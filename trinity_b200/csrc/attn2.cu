@@ -303,17 +303,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
         if (!mbar_wait(&v_full[vpos & 1], (vpos >> 1) & 1, ctx, 405)) { ok = false; break; }
         tc_fence_after();
         if (j + 1 < cur.nt_max) {
+          // Every barrier wait and every commit costs this warp about 200 cycles, and whatever stands between the
+          // arrival of P_t and the issue of S_t(j+1) is on the critical path of query tile t: the K tile is waited
+          // for before P, and the V stage is released after the last S.
+          if (!need_k()) { ok = false; break; }
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (j < cur.nt[t] && !do_pv(t, j)) { ok = false; break; }
-            if (t == 1) umma_commit_warp(&v_empty[vpos & 1]);
             if (j + 1 < cur.nt[t]) {
-              if (!need_k()) { ok = false; break; }
               issue_s(t);
               if (j + 2 == cur.nt[t]) umma_commit_warp(&q_empty[t]);  // that was the item's last read of Q_t
             }
           }
           if (!ok) break;
+          umma_commit_warp(&v_empty[vpos & 1]);
           k_step_done();
         } else {  // last step of the item: both P V first, then the first S tiles of the next item
 #pragma unroll
