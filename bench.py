@@ -46,6 +46,11 @@ WORKLOADS = {
     "llama3_8b_vanilla_prefill_b2_s2048": dict(B=2, S=2048, N=4096, Hq=32, Hkv=8, D=128, variant="vanilla"),   # profiling size
     "tiny": dict(B=2, S=256, N=512, Hq=4, Hkv=2, D=128, variant="vanilla"),
     # FFN blocks: M tokens, N hidden, P inner
+    "llama3_8b_kv_evict_b16_l8192_k4096": dict(kind="evict", B=16, Hkv=32, L=8192, D=128, topk=4096, recent=0),
+    "llama3_8b_kv_evict_b4_l4096_k1024": dict(kind="evict", B=4, Hkv=32, L=4096, D=128, topk=1024, recent=64),   # after cfg 4
+    # grouped-query caches: a cache row keeps what any of the 4 q heads of its group selected (4 lists per row)
+    "llama3_8b_gqa_kv_evict_b16_l8192_k2048": dict(kind="evict", B=16, Hkv=8, group=4, L=8192, D=128, topk=2048, recent=128),
+    "falcon_7b_kv_evict_b16_l2048_k1024": dict(kind="evict", B=16, Hkv=71, L=2048, D=64, topk=1024, recent=0),
     "llama3_8b_swiglu_ffn_m64": dict(kind="ffn", M=64, N=4096, P=14336, act="swiglu", dtype="fp16"),
     "llama3_8b_swiglu_ffn_m16384": dict(kind="ffn", M=16384, N=4096, P=14336, act="swiglu", dtype="bf16"),
     "falcon_7b_gelu_ffn_m32768": dict(kind="ffn", M=32768, N=4544, P=18176, act="gelu", dtype="bf16"),
@@ -355,6 +360,110 @@ def run_ffn(args, w, name):
         dist.destroy_process_group()
 
 
+def run_evict(args, w, name):
+    """KV-cache eviction (top-k index lists -> packed caches), an HBM-bound step: every rank packs the caches of its own
+    batch (no collective, weak scaling).  Algorithmic bytes = kept positions x head_dim x 2 B x (K, V) x (read + write)."""
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    from trinity_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, H, Lc, D, topk, recent = (w[k] for k in ("B", "Hkv", "L", "D", "topk", "recent"))
+    group = w.get("group", 1)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    k = torch.randn(B, H, Lc, D, generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn(B, H, Lc, D, generator=gen, device=dev).to(torch.bfloat16)
+    # one top-k list per q head (distinct positions, score order); the lists of a group lie one after the other
+    idx = ops.topk(torch.randn(B, H * group, Lc, generator=gen, device=dev), topk).view(B, H, group * topk)
+    k_dst, v_dst, pos, n = ops.kv_compact(k, v, idx, Lc, recent)
+    kept = int(n.sum())
+    algo_bytes = kept * D * 2 * 2 * 2
+
+    def step():
+        ops.kv_compact(k, v, idx, Lc, recent, k_dst=k_dst, v_dst=v_dst, kept_pos=pos, new_len=n)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    ops.device_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    # end to end: the index lists come from pinned host memory, the kept positions and counts go back
+    idx_host = idx.cpu().pin_memory()
+    pos_host, n_host = torch.empty(pos.shape, dtype=torch.int32).pin_memory(), torch.empty(n.shape, dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        idx.copy_(idx_host, non_blocking=True)
+        step()
+        pos_host.copy_(pos, non_blocking=True)
+        n_host.copy_(n, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    ops.device_status()
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    if rank == 0:
+        peaks = load_peaks()
+        gbs = algo_bytes / (ms * 1e-3) / 1e9
+        line = {
+            "metric": "kv_evict_gbs", "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16 (bf16 moved as bits)",
+            "data": "synthetic",
+            "config": {"workload": name, "batch_per_gpu": B, "kv_heads": H, "q_heads_per_kv_head": group, "cache_len": Lc, "head_dim": D, "topk": topk,
+                       "keep_recent": recent, "kept_positions": kept,
+                       "l2": f"source caches {2 * B * H * Lc * D * 2 / 1e6:.0f} MB + destination {algo_bytes / 2e6:.0f} MB (> 126 MB L2)"},
+            "e2e": {"value": algo_bytes * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": idx.numel() * 4, "d2h_bytes_per_step": (pos.numel() + n.numel()) * 4, "api": "ops.kv_compact"},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "kernel": "kv_compact_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_launch": algo_bytes,
+                         "traffic": None, "ms_per_launch": ms},
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count())
+            kc, vc, ic = k[0].cpu(), v[0].cpu(), idx[0].cpu()
+            t0 = time.perf_counter()
+            _, _, _, nc = orc.kv_compact(kc, vc, ic, Lc, recent)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": int(nc.sum()) * D * 8 / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                    "seconds": dt, "sample": f"1 of {B} sequences ({H} cache rows), 1 pass, oracle port"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,6 +477,10 @@ def main():
                          "KV-head groups dealt out over the ranks (strong scaling)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
+    if w.get("kind") == "evict":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the attention workloads")
+        return run_evict(args, w, args.workload)
     if w.get("kind") == "ffn":
         if args.impl == "reference":
             raise SystemExit("--impl reference is defined for the attention workloads")

@@ -183,6 +183,43 @@ int tb200_ffn_forward(const tb200_ffn_args* args, void* stream);
  * selects keys); n <= 16384, 1 <= k <= n. */
 int tb200_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * KV-cache eviction: pack the cache positions an index list names to the front of a destination
+ * cache.  New relative to the reference: its KeyFormer / RoCo modules emit the per-key scores
+ * (`C_out`, `C_out1`, `C_out2`: evaluation/keyformer/keyformer_falcon_benchmark4358.py:19-147,
+ * evaluation/roco/roco_falcon_benchmark1620.py:19-141) and nothing consumes them; this is the
+ * consumer, on the reference's cache layout `(H, P+M, D)` (convert_eval_rms.py:82-83) with rows =
+ * batch * kv heads.
+ *
+ * For every cache row r: keep = { idx[r,i] : 0 <= idx[r,i] < kv_len } united with the recent
+ * window [kv_len - keep_recent, kv_len); the kept positions p_0 < p_1 < ... (ascending, duplicates
+ * counted once) give k_dst[r, j, :] = k_src[r, p_j, :], v likewise, new_len[r] = their count,
+ * kept_pos[r, j] = p_j and -1 for j >= new_len[r].  Destination positions >= new_len[r] are left
+ * untouched.  idx may hold several lists per row (GQA: the lists of the q heads of a group, one
+ * after the other: n_idx = group * k) - a position any of them names is kept.  Bit-exact, no
+ * workspace.  Source and destination must not overlap; head_dim 64 or 128, 16-bit elements,
+ * kv_len <= 262144, rows <= 65535, dst_cache_len >= tb200_kv_compact_max_keep(). */
+typedef struct {
+  int dtype;                 /* TB200_F16 or TB200_BF16 (only the element size matters) */
+  int rows;                  /* batch * kv heads */
+  int head_dim;
+  int kv_len;                /* valid positions per source row */
+  int src_cache_len;         /* positions per source row (row pitch) */
+  int dst_cache_len;         /* positions per destination row */
+  int n_idx;                 /* indices per row */
+  int keep_recent;           /* the last keep_recent positions are kept whatever idx says */
+  const int32_t* idx;        /* (rows, n_idx); entries outside [0, kv_len) are ignored */
+  const void* k_src;         /* (rows, src_cache_len, head_dim) */
+  const void* v_src;
+  void* k_dst;               /* (rows, dst_cache_len, head_dim) */
+  void* v_dst;
+  int32_t* kept_pos;         /* (rows, tb200_kv_compact_max_keep()) out, or NULL */
+  int32_t* new_len;          /* (rows) out, or NULL */
+} tb200_kv_compact_args;
+/* min(kv_len, n_idx + keep_recent): the most positions a row can keep, and the width of kept_pos. */
+int64_t tb200_kv_compact_max_keep(const tb200_kv_compact_args* args);
+int tb200_kv_compact(const tb200_kv_compact_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,7 +28,8 @@ golden vectors in ``tests/test_oracle.py``).
 Parity status: pinned at the reference parameter point by golden vectors
 generated from the reference classes.  UNPINNED (nothing in the reference
 computes them): GELU MLP, top-k indices, causal masking, softmax scale,
-GQA/MQA, norm weight/eps, tau != 1.5, column variance.
+GQA/MQA, norm weight/eps, tau != 1.5, column variance, KV-cache eviction
+(``kv_compact``: the reference stops at the per-key scores).
 """
 from __future__ import annotations
 
@@ -55,6 +56,41 @@ def stable_topk(scores: torch.Tensor, k: int) -> torch.Tensor:
     """First ``k`` indices of a stable descending sort along the last axis (ties -> lower index)."""
     order = torch.sort(scores, dim=-1, descending=True, stable=True).indices
     return order[..., :k].to(torch.int32)
+
+
+def kv_compact(k: torch.Tensor, v: torch.Tensor, idx: torch.Tensor, kv_len: int, keep_recent: int = 0):
+    """Eviction step after the per-key scores: per cache row keep the positions ``idx`` names (entries outside
+    ``[0, kv_len)`` ignored, duplicates once) and the last ``keep_recent`` ones, packed in ascending position order.
+
+    ``k, v``: ``(..., L, D)``; ``idx``: integer ``(..., n_idx)``.  Returns ``(k_out, v_out, kept_pos, new_len)`` with
+    ``k_out, v_out`` ``(..., max_keep, D)`` zero beyond each row's count, ``kept_pos`` ``(..., max_keep)`` padded
+    with -1, ``max_keep = min(kv_len, n_idx + keep_recent)``.  Plain loops over rows: parity unpinned (the reference
+    defines the layout, ``convert_eval_rms.py:82-83``, and the scores, never the eviction)."""
+    lead = k.shape[:-2]
+    L, D = k.shape[-2], k.shape[-1]
+    n_idx = idx.shape[-1]
+    max_keep = min(kv_len, n_idx + keep_recent)
+    k2, v2 = k.reshape(-1, L, D), v.reshape(-1, L, D)
+    rows = k2.shape[0]
+    i2 = idx.reshape(rows, n_idx).to(torch.int64)
+    k_out = torch.zeros(rows, max_keep, D, dtype=k.dtype)
+    v_out = torch.zeros(rows, max_keep, D, dtype=v.dtype)
+    kept = torch.full((rows, max_keep), -1, dtype=torch.int32)
+    new_len = torch.zeros(rows, dtype=torch.int32)
+    for r in range(rows):
+        keep = torch.zeros(kv_len, dtype=torch.bool)
+        ok = i2[r][(i2[r] >= 0) & (i2[r] < kv_len)]
+        keep[ok] = True
+        if keep_recent > 0:
+            keep[max(kv_len - keep_recent, 0):] = True
+        pos = torch.nonzero(keep).flatten()
+        n = pos.numel()
+        k_out[r, :n] = k2[r, pos]
+        v_out[r, :n] = v2[r, pos]
+        kept[r, :n] = pos.to(torch.int32)
+        new_len[r] = n
+    return (k_out.reshape(*lead, max_keep, D), v_out.reshape(*lead, max_keep, D), kept.reshape(*lead, max_keep),
+            new_len.reshape(*lead) if lead else new_len.reshape(()))
 
 
 def attention_block(

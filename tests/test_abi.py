@@ -39,14 +39,16 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 def test_struct_layout_matches_header(tmp_path):
     from trinity_b200 import _lib
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "trinity_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "trinity_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    'sizeof(tb200_gemm_args),sizeof(tb200_attn_args),sizeof(tb200_ffn_args),'
-                   'offsetof(tb200_attn_args,workspace),offsetof(tb200_ffn_args,w_down),offsetof(tb200_gemm_args,split_k));}')
+                   'offsetof(tb200_attn_args,workspace),offsetof(tb200_ffn_args,w_down),offsetof(tb200_gemm_args,split_k),'
+                   'sizeof(tb200_kv_compact_args),offsetof(tb200_kv_compact_args,new_len));}')
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
     got = [int(v) for v in subprocess.check_output([str(exe)]).split()]
     want = [C.sizeof(_lib.GemmArgs), C.sizeof(_lib.AttnArgs), C.sizeof(_lib.FfnArgs),
-            _lib.AttnArgs.workspace.offset, _lib.FfnArgs.w_down.offset, _lib.GemmArgs.split_k.offset]
+            _lib.AttnArgs.workspace.offset, _lib.FfnArgs.w_down.offset, _lib.GemmArgs.split_k.offset,
+            C.sizeof(_lib.KvCompactArgs), _lib.KvCompactArgs.new_len.offset]
     assert got == want
 
 
@@ -67,6 +69,9 @@ def test_calls_fail_loudly_without_a_gpu(lib):
     assert lib.tb200_attn_forward(C.byref(a), None) != 0
     f = _lib.FfnArgs(dtype=_lib.BF16)
     assert lib.tb200_ffn_forward(C.byref(f), None) != 0
+    e = _lib.KvCompactArgs(dtype=_lib.BF16, rows=1, head_dim=128, kv_len=8, src_cache_len=8, dst_cache_len=8, n_idx=2)
+    assert lib.tb200_kv_compact_max_keep(C.byref(e)) == 2      # pure host arithmetic: answers without a device
+    assert lib.tb200_kv_compact(C.byref(e), None) != 0
 
 
 def test_ops_reject_cpu_tensors(lib):

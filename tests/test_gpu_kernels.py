@@ -96,3 +96,105 @@ def test_topk_handles_zero_signs_and_rejects_oversize(ops):
     assert ops.topk(s.to(dev()), 5).cpu().tolist() == [[3, 0, 1, 2, 4]]
     with pytest.raises(Tb200Error):
         ops.topk(torch.zeros(1, 20000, device=dev()), 4)
+
+
+# ------------------------------------------------------------------------------------------------- KV-cache eviction
+def _evict_case(lead, L, kv_len, D, n_idx, keep_recent, dt, seed, junk=True):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(*lead, L, D, generator=g).to(dt)
+    v = torch.randn(*lead, L, D, generator=g).to(dt)
+    idx = torch.randint(0, max(kv_len, 1), (*lead, n_idx), generator=g, dtype=torch.int32)   # with duplicates
+    if junk and n_idx >= 4:
+        idx[..., 0] = -3
+        idx[..., 1] = kv_len          # first invalid position
+        idx[..., 2] = 2 ** 31 - 1
+    return k, v, idx
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("lead,L,kv_len,D,n_idx,recent", [
+    ((1,), 64, 64, 128, 16, 0),            # one CTA per row
+    ((2, 3), 200, 137, 64, 40, 9),         # ragged: kv_len not a multiple of 32, recent window inside a bitmap word
+    ((4, 8), 1040, 1040, 128, 256, 32),    # the reference's decode cache (P 1024 + M 16), GQA-sized rows
+    ((71,), 1040, 1040, 64, 512, 0),       # Falcon heads
+    ((2, 2), 4352, 4100, 128, 3000, 500),  # many chunks per row, keeps most of the cache
+    ((3,), 96, 50, 128, 200, 0),           # more indices than positions: everything named survives once
+    ((2,), 300, 300, 64, 0, 70),           # no index list at all: the recent window alone
+])
+def test_kv_compact_matches_oracle(ops, dt, lead, L, kv_len, D, n_idx, recent):
+    k, v, idx = _evict_case(lead, L, kv_len, D, n_idx, recent, dt, seed=L + n_idx)
+    rk, rv, rpos, rlen = orc.kv_compact(k, v, idx, kv_len, recent)
+    max_keep = rpos.shape[-1]
+    # destination rows longer than needed and pre-filled: positions beyond the kept count must stay untouched
+    k_dst = torch.full((*lead, max_keep + 5, D), 7.0, dtype=dt, device=dev())
+    v_dst = torch.full((*lead, max_keep + 5, D), -7.0, dtype=dt, device=dev())
+    gk, gv, gpos, glen = ops.kv_compact(k.to(dev()), v.to(dev()), idx.to(dev()), kv_len, recent, k_dst=k_dst, v_dst=v_dst)
+    ops.device_status()
+    assert torch.equal(glen.cpu(), rlen) and torch.equal(gpos.cpu(), rpos)
+    live = (torch.arange(max_keep + 5).expand(*lead, -1) < rlen.unsqueeze(-1)).unsqueeze(-1)
+    pad = lambda t, fill: torch.cat([t, torch.zeros(*lead, 5, D, dtype=dt)], dim=-2).where(live, torch.tensor(fill, dtype=dt))
+    assert torch.equal(gk.cpu(), pad(rk, 7.0)) and torch.equal(gv.cpu(), pad(rv, -7.0))
+
+
+def test_kv_compact_after_topk_keeps_the_best_keys(ops):
+    """The chain the blocks feed: per-key scores -> top-k -> eviction; the kept set is the top-k set, in cache order."""
+    g = torch.Generator().manual_seed(3)
+    H, Lc, D, topk = 8, 1040, 128, 128
+    scores = torch.randn(H, Lc, generator=g)
+    k, v, _ = _evict_case((H,), Lc, Lc, D, 4, 0, torch.bfloat16, seed=4)
+    idx = ops.topk(scores.to(dev()), topk)
+    gk, gv, gpos, glen = ops.kv_compact(k.to(dev()), v.to(dev()), idx, Lc)
+    assert glen.cpu().tolist() == [topk] * H
+    want = torch.sort(orc.stable_topk(scores, topk).long(), dim=-1).values
+    assert torch.equal(gpos.cpu().long(), want)
+    assert torch.equal(gk.cpu(), torch.gather(k, 1, want.unsqueeze(-1).expand(-1, -1, D)))
+    assert torch.equal(gv.cpu(), torch.gather(v, 1, want.unsqueeze(-1).expand(-1, -1, D)))
+
+
+def test_kv_compact_full_size_properties(ops):
+    """RoCo configuration size (B4, 32 heads, 4096+ keys, top-k 1024 + 64 recent): idempotence (evicting again with
+    the identity list changes nothing), keep-all is a copy, and the run is bit-identical when repeated."""
+    B, H, Lc, D, topk, recent = 4, 32, 4096, 128, 1024, 64
+    g = torch.Generator(device=dev()).manual_seed(11)
+    k = torch.randn(B, H, Lc, D, generator=g, device=dev()).to(torch.bfloat16)
+    v = torch.randn(B, H, Lc, D, generator=g, device=dev()).to(torch.bfloat16)
+    scores = torch.randn(B, H, Lc, generator=g, device=dev())
+    idx = ops.topk(scores, topk)
+    k1, v1, pos1, len1 = ops.kv_compact(k, v, idx, Lc, recent)
+    k1b, v1b, pos1b, _ = ops.kv_compact(k, v, idx, Lc, recent)
+    n = len1.long()
+    assert int(n.min()) >= topk and int(n.max()) <= topk + recent
+    valid = torch.arange(pos1.shape[-1], device=dev()).expand_as(pos1) < n.unsqueeze(-1)
+    # destination positions beyond a row's count are left as they were (uninitialised here): compare the packed part
+    assert torch.equal(k1[valid], k1b[valid]) and torch.equal(v1[valid], v1b[valid]) and torch.equal(pos1, pos1b)
+    p = pos1.long().clamp_min(0)
+    assert bool(((pos1 >= 0) == valid).all())
+    assert bool((p[..., 1:] > p[..., :-1])[valid[..., 1:]].all())                      # strictly ascending
+    assert bool((torch.gather(k, 2, p.unsqueeze(-1).expand(-1, -1, -1, D)) == k1)[valid].all())
+    in_topk = torch.zeros(B, H, Lc, dtype=torch.bool, device=dev()).scatter_(2, idx.long(), True)
+    in_topk[..., Lc - recent:] = True
+    assert torch.equal(in_topk.sum(-1), n)
+    # evicting the packed cache with the identity list keeps it as it is (rows share the smallest kept count)
+    m = int(n.min())
+    ident = torch.arange(m, dtype=torch.int32, device=dev()).expand(B, H, m).contiguous()
+    k2, v2, pos2, len2 = ops.kv_compact(k1, v1, ident, m)
+    assert torch.equal(k2, k1[..., :m, :]) and torch.equal(v2, v1[..., :m, :]) and bool((len2 == m).all())
+    ops.device_status()
+
+
+def test_kv_compact_rejects_bad_arguments(ops):
+    from trinity_b200._lib import Tb200Error
+    k, v, idx = (t.to(dev()) for t in _evict_case((2,), 64, 64, 128, 8, 0, torch.bfloat16, seed=1))
+    with pytest.raises(Tb200Error):       # in place
+        ops.kv_compact(k, v, idx, 64, k_dst=k, v_dst=v)
+    with pytest.raises(Tb200Error):       # destination too short
+        ops.kv_compact(k, v, idx, 64, k_dst=torch.empty(2, 4, 128, dtype=k.dtype, device=dev()), v_dst=torch.empty(2, 4, 128, dtype=k.dtype, device=dev()))
+    with pytest.raises(Tb200Error):       # more valid positions than the cache holds
+        ops.kv_compact(k, v, idx, 65)
+    with pytest.raises(Tb200Error):       # head dimension
+        ops.kv_compact(k[..., :32].contiguous(), v[..., :32].contiguous(), idx, 64)
+    with pytest.raises(TypeError):
+        ops.kv_compact(k, v, idx.long(), 64)
+    # nothing to keep: a call that launches nothing and reports zero lengths
+    _, _, pos, n = ops.kv_compact(k, v, idx[:, :0].contiguous(), 64)
+    assert pos.shape == (2, 0) and n.cpu().tolist() == [0, 0]

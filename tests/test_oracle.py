@@ -126,3 +126,18 @@ def test_causal_and_gqa_against_naive():
 def test_stable_topk_ties_prefer_lower_index():
     s = torch.tensor([[1.0, 3.0, 3.0, 0.5, 3.0, 1.0]])
     assert orc.stable_topk(s, 5).tolist() == [[1, 2, 4, 0, 5]]
+
+
+def test_kv_compact_known_answer():
+    """Hand-checked case: duplicates once, out-of-range entries ignored, recent window united, ascending order."""
+    k = torch.arange(2 * 10 * 4, dtype=torch.float32).reshape(2, 10, 4)     # rows 0/1, 10 positions (8 valid), D 4
+    v = -k
+    idx = torch.tensor([[5, 1, 5, 9, -1], [0, 0, 0, 0, 0]], dtype=torch.int32)
+    k_out, v_out, kept, n = orc.kv_compact(k, v, idx, kv_len=8, keep_recent=2)
+    assert kept.tolist() == [[1, 5, 6, 7, -1, -1, -1], [0, 6, 7, -1, -1, -1, -1]]
+    assert n.tolist() == [4, 3]
+    assert torch.equal(k_out[0, :4], k[0, [1, 5, 6, 7]]) and torch.equal(v_out[1, :3], v[1, [0, 6, 7]])
+    assert not k_out[0, 4:].any() and not v_out[1, 3:].any()
+    # keeping everything is the identity on the valid prefix
+    k_all, _, kept_all, n_all = orc.kv_compact(k, v, torch.arange(8, dtype=torch.int32).flip(0).expand(2, 8), kv_len=8)
+    assert torch.equal(k_all, k[:, :8]) and n_all.tolist() == [8, 8] and kept_all[0].tolist() == list(range(8))

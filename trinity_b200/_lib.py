@@ -52,6 +52,15 @@ class FfnArgs(C.Structure):
     ]
 
 
+class KvCompactArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("rows", C.c_int), ("head_dim", C.c_int), ("kv_len", C.c_int),
+        ("src_cache_len", C.c_int), ("dst_cache_len", C.c_int), ("n_idx", C.c_int), ("keep_recent", C.c_int),
+        ("idx", C.c_void_p), ("k_src", C.c_void_p), ("v_src", C.c_void_p), ("k_dst", C.c_void_p), ("v_dst", C.c_void_p),
+        ("kept_pos", C.c_void_p), ("new_len", C.c_void_p),
+    ]
+
+
 # every symbol include/trinity_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "tb200_strerror": (C.c_char_p, [C.c_int]),
@@ -67,6 +76,8 @@ SYMBOLS = {
     "tb200_ffn_workspace_bytes": (C.c_size_t, [C.POINTER(FfnArgs)]),
     "tb200_ffn_forward": (C.c_int, [C.POINTER(FfnArgs), C.c_void_p]),
     "tb200_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "tb200_kv_compact_max_keep": (C.c_int64, [C.POINTER(KvCompactArgs)]),
+    "tb200_kv_compact": (C.c_int, [C.POINTER(KvCompactArgs), C.c_void_p]),
 }
 
 _lib = None

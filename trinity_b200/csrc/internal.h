@@ -160,4 +160,7 @@ int launch_score_colreduce(const ScoreLaunch& s, cudaStream_t stream);
 int launch_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, cudaStream_t stream);
 int launch_cast_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t stream);
 
+// ---------------------------------------------------------------- evict.cu
+int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream);
+
 }  // namespace tb200

@@ -156,6 +156,50 @@ def topk(scores: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> to
     return out
 
 
+def kv_compact(k_src: torch.Tensor, v_src: torch.Tensor, idx: torch.Tensor, kv_len: int, keep_recent: int = 0,
+               k_dst: Optional[torch.Tensor] = None, v_dst: Optional[torch.Tensor] = None, kept_pos: Optional[torch.Tensor] = None,
+               new_len: Optional[torch.Tensor] = None):
+    """Pack the cache positions ``idx`` names (and the last ``keep_recent``) to the front of ``k_dst`` / ``v_dst``.
+
+    ``k_src, v_src``: ``(..., L, D)`` caches, leading axes = batch and kv heads; ``idx``: int32 ``(..., n_idx)`` over the
+    same leading axes.  Returns ``(k_dst, v_dst, kept_pos, new_len)``; destination caches are allocated
+    ``(..., max_keep, D)`` when not given."""
+    lib = L.load()
+    if idx.dtype != torch.int32:
+        raise TypeError("idx must be int32")
+    if k_src.shape != v_src.shape or k_src.dtype != v_src.dtype:
+        raise ValueError("k_src and v_src must agree in shape and dtype")
+    lead = k_src.shape[:-2]
+    if tuple(idx.shape[:-1]) != tuple(lead):
+        raise ValueError(f"idx leading axes {tuple(idx.shape[:-1])} do not match the caches' {tuple(lead)}")
+    rows = 1
+    for d in lead:
+        rows *= int(d)
+    args = L.KvCompactArgs(dtype=_dt(k_src), rows=rows, head_dim=int(k_src.shape[-1]), kv_len=int(kv_len),
+                           src_cache_len=int(k_src.shape[-2]), n_idx=int(idx.shape[-1]), keep_recent=int(keep_recent))
+    max_keep = int(lib.tb200_kv_compact_max_keep(C.byref(args)))
+    dev = k_src.device
+    if k_dst is None:
+        k_dst = torch.empty(*lead, max_keep, k_src.shape[-1], dtype=k_src.dtype, device=dev)
+    if v_dst is None:
+        v_dst = torch.empty(*lead, max_keep, k_src.shape[-1], dtype=k_src.dtype, device=dev)
+    if k_dst.shape != v_dst.shape or k_dst.dtype != k_src.dtype or v_dst.dtype != k_src.dtype:
+        raise ValueError("k_dst and v_dst must agree in shape and share the source dtype")
+    if tuple(k_dst.shape[:-2]) != tuple(lead) or k_dst.shape[-1] != k_src.shape[-1]:
+        raise ValueError("destination caches must have the source's leading axes and head dimension")
+    if kept_pos is None:
+        kept_pos = torch.empty(*lead, max_keep, dtype=torch.int32, device=dev)
+    if new_len is None:
+        new_len = torch.empty(*lead, dtype=torch.int32, device=dev)
+    if kept_pos.dtype != torch.int32 or new_len.dtype != torch.int32 or kept_pos.numel() != rows * max_keep or new_len.numel() != rows:
+        raise ValueError("kept_pos must be int32 (..., max_keep) and new_len int32 (...)")
+    args.dst_cache_len = int(k_dst.shape[-2])
+    args.idx, args.k_src, args.v_src = _ptr(idx), _ptr(k_src), _ptr(v_src)
+    args.k_dst, args.v_dst, args.kept_pos, args.new_len = _ptr(k_dst), _ptr(v_dst), _ptr(kept_pos), _ptr(new_len)
+    L.check(lib.tb200_kv_compact(C.byref(args), _stream()), "tb200_kv_compact")
+    return k_dst, v_dst, kept_pos, new_len
+
+
 def device_status() -> int:
     """Synchronise and return the device error word (0 = healthy); raises on a recorded timeout."""
     code = C.c_int(0)
