@@ -4,15 +4,15 @@ and write the reference's result records.
 Mirrors ``benchmark/*_benchmark.py`` of the reference (one script per block family and model there, one class here):
 
 * IR files hold one candidate per line, ``<id>: <expression>``; lines without a numeric id and expressions containing
-  ``dummydata`` are skipped (``benchmark/vanilla_llama_benchmark.py:140-160``).
+  ``dummydata`` are skipped (``benchmark/vanilla_llama_benchmark.py:141-162``).
 * Tensors are fp16; inputs are ``randn.clamp(-1, 1) * scale`` (scale 0.01 for the attention families, 0.001 for the FFN
   families), outputs and intermediates are zeros (``benchmark/vanilla_llama_benchmark.py:131-138``,
-  ``benchmark/ffn_llama_benchmark.py:100-110``).  A parameter a candidate lists that the table lacks is an error of that
+  ``benchmark/ffn_llama_benchmark.py:97-110``).  A parameter a candidate lists that the table lacks is an error of that
   candidate, recorded in its row, as in the reference.
 * Timing: one call outside capture, ten warm-ups on a side stream, CUDA-graph capture of ``forward(*args)``, a hundred
   replays between CUDA events (``benchmark/vanilla_llama_benchmark.py:223-301``).
 * Records: ``{ir_id, ir_expression, execution_time_ms, tensor_config, error}`` written after every configuration
-  (``benchmark/vanilla_llama_benchmark.py:388-401,513-540``); a failed candidate has ``execution_time_ms = inf``
+  (``benchmark/vanilla_llama_benchmark.py:388-401,517-546``); a failed candidate has ``execution_time_ms = inf``
   (JSON ``Infinity``, as Python's ``json`` writes it) and the exception text in ``error``.
 
     python -m trinity_b200.sweep --family roco --configs evaluation/llama_configs.json \\
