@@ -8,9 +8,9 @@
 // One CTA packs a span of 64 x G destination positions of one cache row (one (batch, kv head)); G (1..16) grows with
 // the amount of work so that the per-CTA preamble below is paid once per several groups while the grid still fills
 // the SMs.  The CTA rebuilds the row's keep-bitmap in shared memory from the index list (the list is a few KB and
-// stays in L2; duplicates and out-of-range entries fall out of the bitmap for free), counts the kept positions before each bitmap word (a block-wide exclusive scan), finds the source positions
-// of its slots, and moves their K and V vectors with 16-byte loads and stores, all loads of a thread in flight
-// before its first store.  No atomics on global memory, no floating-point arithmetic: the result is bit-exact and
+// stays in L2; duplicates and out-of-range entries fall out of the bitmap for free), counts the kept positions before
+// each bitmap word (a block-wide exclusive scan), finds the source positions of its slots, and moves their K and V
+// vectors with 16-byte loads and stores, all loads of a thread in flight before its first store.  No atomics on global memory, no floating-point arithmetic: the result is bit-exact and
 // the same on every run.
 #include <cstdlib>
 
