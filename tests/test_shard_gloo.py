@@ -129,6 +129,43 @@ def test_head_group_sharded_attention_two_ranks():
     torch.testing.assert_close(c1_rank0, want["C_out1"][:, :2], rtol=1e-5, atol=1e-6)   # rank 0 owns q heads 0..1
 
 
+def _evict_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        k, v, idx = _evict_inputs()
+        out = shard.evict_rows(k, v, idx, kv_len=40, keep_recent=3, compact=orc.kv_compact)
+        ret.put((rank, out["rows"].start, out["rows"].stop, out["k"].clone(), out["kept_pos"].clone(), out["all_new_len"].clone()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _evict_inputs():
+    g = torch.Generator().manual_seed(9)
+    rows, L, D = 5, 48, 8          # 5 rows over 2 ranks: shares of 3 and 2
+    return (torch.randn(rows, L, D, generator=g), torch.randn(rows, L, D, generator=g),
+            torch.randint(-2, 44, (rows, 12), generator=g, dtype=torch.int32))
+
+
+def test_row_sharded_eviction_two_ranks():
+    ctx = mp.get_context("spawn")
+    ret = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_evict_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted([ret.get(), ret.get()], key=lambda g: g[0])
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    k, v, idx = _evict_inputs()
+    wk, _, wpos, wlen = orc.kv_compact(k, v, idx, 40, 3)
+    assert [(g[1], g[2]) for g in got] == [(0, 3), (3, 5)]
+    for _, lo, hi, gk, gpos, all_len in got:
+        assert torch.equal(gk, wk[lo:hi]) and torch.equal(gpos, wpos[lo:hi])
+        assert torch.equal(all_len, wlen)            # every rank ends up with every row's new length
+
+
 def test_slices_and_errors():
     qs, kvs = shard.head_group_slices(32, 8, 128, rank=3, world=4)
     assert (qs.start, qs.stop, kvs.start, kvs.stop) == (3 * 8 * 128, 4 * 8 * 128, 3 * 2 * 128, 4 * 2 * 128)

@@ -6,6 +6,8 @@ the plumbing.  The reference has no multi-GPU path at all; the blocks are cut wh
   the per-key outputs; ``x`` is replicated.  No collective: ``O2`` comes out column-sharded ``(T, Hq*D/g)``, which is
   what a row-parallel ``WO`` consumes.  An all-gather is offered for callers that want the full ``O2``.
 * attention with one KV head (Falcon MQA): by **batch** -- no collective, weights replicated.
+* KV eviction: by **cache row** (batch x KV head) -- every rank packs its own contiguous share of the rows; the only
+  exchange is an optional all-gather of the new row lengths (4 bytes per row), which a scheduler needs in full.
 * FFN: tensor-parallel.  Gate/up (or W1) are column-parallel over the inner width, the activation is local, the down
   projection is row-parallel and ends in ONE all-reduce (sum) of ``(T, N)``.  With the ``WO`` prologue, ``WO`` is
   row-parallel on the column-sharded ``O2`` and needs its own all-reduce before the norm, so that the row statistic
@@ -153,3 +155,33 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
     if not falcon_tail:
         return {"FF2": ff2, "attn_O2": a}
     return {"O_FF": ff2, "O_FF_norm": lo.rmsnorm(ff2, None, 0.0), "attn_O2": a}
+
+
+def evict_rows(k_cache: torch.Tensor, v_cache: torch.Tensor, idx: torch.Tensor, kv_len: int, keep_recent: int = 0, *,
+               compact: Optional[Callable] = None, gather_lengths: bool = True, group=None) -> Dict[str, torch.Tensor]:
+    """KV eviction over the ranks: ``k_cache, v_cache (rows, L, D)`` and ``idx (rows, n_idx)`` are the SAME on every
+    rank's call in shape (each rank may hold only its own rows' data); rank r packs rows ``batch_slice(rows, r, world)``
+    with ``compact`` (default ``trinity_b200.ops.kv_compact``) and returns its share: ``rows`` (the slice), ``k``, ``v``,
+    ``kept_pos``, ``new_len``; with ``gather_lengths`` also ``all_new_len (rows,)`` from one all-gather."""
+    rank, world = _world(group)
+    if k_cache.dim() != 3 or idx.dim() != 2 or idx.shape[0] != k_cache.shape[0]:
+        raise ValueError("evict_rows takes (rows, L, D) caches and (rows, n_idx) index lists")
+    if compact is None:
+        from . import ops
+        compact = ops.kv_compact
+    rows = k_cache.shape[0]
+    mine = batch_slice(rows, rank, world)
+    k_new, v_new, kept, n_new = compact(k_cache[mine].contiguous(), v_cache[mine].contiguous(), idx[mine].contiguous(), kv_len, keep_recent)
+    out = {"rows": mine, "k": k_new, "v": v_new, "kept_pos": kept, "new_len": n_new}
+    if gather_lengths:
+        if world == 1:
+            out["all_new_len"] = n_new.clone()
+        else:  # shares differ by at most one row: pad to the largest share, gather, cut
+            width = (rows + world - 1) // world
+            padded = torch.zeros(width, dtype=n_new.dtype, device=n_new.device)
+            padded[: n_new.numel()] = n_new
+            parts = [torch.empty_like(padded) for _ in range(world)]
+            dist.all_gather(parts, padded, group=group)
+            out["all_new_len"] = torch.cat([parts[r][: (s_.stop - s_.start)] for r in range(world)
+                                            for s_ in [batch_slice(rows, r, world)]])
+    return out
