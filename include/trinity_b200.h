@@ -197,8 +197,10 @@ int tb200_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, vo
  * kept_pos[r, j] = p_j and -1 for j >= new_len[r].  Destination positions >= new_len[r] are left
  * untouched.  idx may hold several lists per row (GQA: the lists of the q heads of a group, one
  * after the other: n_idx = group * k) - a position any of them names is kept.  Bit-exact, no
- * workspace.  Source and destination must not overlap; head_dim 64 or 128, 16-bit elements,
- * kv_len <= 262144, rows <= 65535, dst_cache_len >= tb200_kv_compact_max_keep(). */
+ * workspace.  In place: pass k_dst == k_src, v_dst == v_src and dst_cache_len == src_cache_len
+ * (one CTA per row packs front to back); any other overlap of source and destination is refused.
+ * head_dim 64 or 128, 16-bit elements, kv_len <= 262144, rows <= 65535,
+ * dst_cache_len >= tb200_kv_compact_max_keep(). */
 typedef struct {
   int dtype;                 /* TB200_F16 or TB200_BF16 (only the element size matters) */
   int rows;                  /* batch * kv heads */

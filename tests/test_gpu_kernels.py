@@ -136,6 +136,26 @@ def test_kv_compact_matches_oracle(ops, dt, lead, L, kv_len, D, n_idx, recent):
     assert torch.equal(gk.cpu(), pad(rk, 7.0)) and torch.equal(gv.cpu(), pad(rv, -7.0))
 
 
+@pytest.mark.parametrize("lead,L,kv_len,D,n_idx,recent", [
+    ((2, 3), 200, 137, 64, 40, 9), ((4, 8), 1040, 1040, 128, 256, 32), ((2, 2), 4352, 4100, 128, 3000, 500),
+    ((3,), 96, 50, 128, 200, 0), ((2,), 300, 300, 64, 0, 70), ((1,), 512, 512, 128, 512, 0),
+])
+def test_kv_compact_in_place(ops, lead, L, kv_len, D, n_idx, recent):
+    """Source and destination the same caches: packed prefix as the oracle's, everything behind it as it was."""
+    k, v, idx = _evict_case(lead, L, kv_len, D, n_idx, recent, torch.bfloat16, seed=L * 3 + n_idx, junk=n_idx != 512)
+    if n_idx == 512:
+        idx = torch.arange(512, dtype=torch.int32).flip(0).expand(*lead, 512).contiguous()   # keep all: nothing moves
+    rk, rv, rpos, rlen = orc.kv_compact(k, v, idx, kv_len, recent)
+    kd, vd = k.to(dev()), v.to(dev())
+    gk, gv, gpos, glen = ops.kv_compact(kd, vd, idx.to(dev()), kv_len, recent, k_dst=kd, v_dst=vd)
+    ops.device_status()
+    assert gk.data_ptr() == kd.data_ptr()
+    assert torch.equal(glen.cpu(), rlen) and torch.equal(gpos.cpu(), rpos)
+    live = (torch.arange(L).expand(*lead, -1) < rlen.unsqueeze(-1)).unsqueeze(-1)
+    grow = lambda t: torch.cat([t, torch.zeros(*lead, L - t.shape[-2], D, dtype=t.dtype)], dim=-2)
+    assert torch.equal(gk.cpu(), torch.where(live, grow(rk), k)) and torch.equal(gv.cpu(), torch.where(live, grow(rv), v))
+
+
 def test_kv_compact_after_topk_keeps_the_best_keys(ops):
     """The chain the blocks feed: per-key scores -> top-k -> eviction; the kept set is the top-k set, in cache order."""
     g = torch.Generator().manual_seed(3)
@@ -185,8 +205,11 @@ def test_kv_compact_full_size_properties(ops):
 def test_kv_compact_rejects_bad_arguments(ops):
     from trinity_b200._lib import Tb200Error
     k, v, idx = (t.to(dev()) for t in _evict_case((2,), 64, 64, 128, 8, 0, torch.bfloat16, seed=1))
-    with pytest.raises(Tb200Error):       # in place
-        ops.kv_compact(k, v, idx, 64, k_dst=k, v_dst=v)
+    with pytest.raises(Tb200Error):       # overlapping, but not the same caches: K packed into V's memory
+        ops.kv_compact(k, v, idx, 64, k_dst=v, v_dst=torch.empty_like(v))
+    buf = torch.zeros(3, 64, 128, dtype=k.dtype, device=dev())
+    with pytest.raises(Tb200Error):       # destination rows start inside the source rows
+        ops.kv_compact(buf[0:2], v, idx, 64, k_dst=buf[1:3], v_dst=torch.empty_like(v))
     with pytest.raises(Tb200Error):       # destination too short
         ops.kv_compact(k, v, idx, 64, k_dst=torch.empty(2, 4, 128, dtype=k.dtype, device=dev()), v_dst=torch.empty(2, 4, 128, dtype=k.dtype, device=dev()))
     with pytest.raises(Tb200Error):       # more valid positions than the cache holds

@@ -38,20 +38,12 @@ struct EvictParams {
   long long src_pitch, dst_pitch;  // 16-byte units per cache row of the source / destination
 };
 
-// VEC: 16-byte units per position (head_dim * 2 / 16)
-template <int VEC>
-__global__ void __launch_bounds__(kEvictThreads) kv_compact_kernel(const EvictParams p) {
-  extern __shared__ uint32_t evict_smem[];
-  uint32_t* bitmap = evict_smem;  // [words]
-  __shared__ int src_pos[kEvictSlots * kEvictMaxGroups];
-  __shared__ uint32_t warp_sums[kEvictThreads / 32];
-  __shared__ uint32_t total_s;
-
+// The keep-bitmap of cache row `row` in shared memory (index list united with the recent window) and the block-wide
+// exclusive count of kept positions: returns the number of kept positions before the run of words [*w_begin, *w_end)
+// this thread owns; *total (shared) holds the row's count.  Ends with a barrier: bitmap and *total are readable.
+__device__ __forceinline__ uint32_t keep_bitmap(const EvictParams& p, long long row, uint32_t* bitmap, uint32_t* warp_sums,
+                                                uint32_t* total, int* w_begin_out, int* w_end_out) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const long long row = blockIdx.y;
-  const int span = p.groups * kEvictSlots;
-  const int slot0 = blockIdx.x * span;
-
   for (int w = tid; w < p.words; w += kEvictThreads) {
     // the recent window [kv_len - keep_recent, kv_len) is written as whole-word masks
     const int lo = max(p.kv_len - p.keep_recent, 0) - w * 32, hi = p.kv_len - w * 32;
@@ -63,7 +55,6 @@ __global__ void __launch_bounds__(kEvictThreads) kv_compact_kernel(const EvictPa
     }
     bitmap[w] = m;
   }
-  for (int s = tid; s < span; s += kEvictThreads) src_pos[s] = -1;
   __syncthreads();
   const int32_t* my_idx = p.idx + row * p.n_idx;
   for (int i = tid; i < p.n_idx; i += kEvictThreads) {
@@ -94,10 +85,31 @@ __global__ void __launch_bounds__(kEvictThreads) kv_compact_kernel(const EvictPa
       if (lane >= d) s += up;
     }
     if (lane < kEvictThreads / 32) warp_sums[lane] = s - v;  // exclusive
-    if (lane == kEvictThreads / 32 - 1) total_s = s;
+    if (lane == kEvictThreads / 32 - 1) *total = s;
   }
   __syncthreads();
-  uint32_t run = warp_sums[warp] + incl - mine;
+  *w_begin_out = w_begin;
+  *w_end_out = w_end;
+  return warp_sums[warp] + incl - mine;
+}
+
+// VEC: 16-byte units per position (head_dim * 2 / 16)
+template <int VEC>
+__global__ void __launch_bounds__(kEvictThreads) kv_compact_kernel(const EvictParams p) {
+  extern __shared__ uint32_t evict_smem[];
+  uint32_t* bitmap = evict_smem;  // [words]
+  __shared__ int src_pos[kEvictSlots * kEvictMaxGroups];
+  __shared__ uint32_t warp_sums[kEvictThreads / 32];
+  __shared__ uint32_t total_s;
+
+  const int tid = threadIdx.x;
+  const long long row = blockIdx.y;
+  const int span = p.groups * kEvictSlots;
+  const int slot0 = blockIdx.x * span;
+
+  for (int s = tid; s < span; s += kEvictThreads) src_pos[s] = -1;
+  int w_begin, w_end;
+  uint32_t run = keep_bitmap(p, row, bitmap, warp_sums, &total_s, &w_begin, &w_end);
   for (int w = w_begin; w < w_end; ++w) {
     const uint32_t bits = bitmap[w];
     const uint32_t cnt = __popc(bits);
@@ -155,6 +167,77 @@ __global__ void __launch_bounds__(kEvictThreads) kv_compact_kernel(const EvictPa
   }
 }
 
+// The same packing inside the source caches.  A packed position never lies behind its source (slot j <= p_j), so a
+// row can be packed front to back by ONE CTA: rounds of 128 slots, every load of a round done (block barrier) before
+// its first store; a later round's sources lie behind everything earlier rounds wrote.  Slots that are already in
+// place (the kept prefix of a row) are neither read nor written.  One CTA per row: the grid fills the GPU only with
+// a few hundred cache rows, which is what a batch of sequences has.
+constexpr int kInplaceSlots = 128;
+
+template <int VEC>
+__global__ void __launch_bounds__(kEvictThreads) kv_compact_inplace_kernel(const EvictParams p) {
+  extern __shared__ uint32_t evict_smem[];
+  uint32_t* bitmap = evict_smem;  // [words]
+  __shared__ int src_pos[kInplaceSlots];
+  __shared__ uint32_t warp_sums[kEvictThreads / 32];
+  __shared__ uint32_t total_s;
+
+  const int tid = threadIdx.x;
+  const long long row = blockIdx.x;
+  int w_begin, w_end;
+  const uint32_t run0 = keep_bitmap(p, row, bitmap, warp_sums, &total_s, &w_begin, &w_end);
+  const int n_kept = static_cast<int>(total_s);
+  uint32_t run_end = run0;  // kept positions before the end of this thread's run of words
+  for (int w = w_begin; w < w_end; ++w) run_end += __popc(bitmap[w]);
+  if (tid == 0 && p.new_len != nullptr) p.new_len[row] = n_kept;
+  if (p.kept_pos != nullptr) {
+    uint32_t dest = run0;
+    for (int w = w_begin; w < w_end; ++w)
+      for (uint32_t rest = bitmap[w]; rest != 0u; rest &= rest - 1u) p.kept_pos[row * p.max_keep + dest++] = w * 32 + __ffs(rest) - 1;
+    for (int s = n_kept + tid; s < p.max_keep; s += kEvictThreads) p.kept_pos[row * p.max_keep + s] = -1;
+  }
+
+  constexpr int kUnits = kInplaceSlots * VEC;
+  constexpr int kPerThread = kUnits / kEvictThreads;
+  uint4* kc = p.k_dst + row * p.dst_pitch;
+  uint4* vc = p.v_dst + row * p.dst_pitch;
+  for (int g0 = 0; g0 < n_kept; g0 += kInplaceSlots) {
+    // sources of the slots [g0, g0 + 128): every thread whose run of words holds some of them walks that run
+    if (run_end > static_cast<uint32_t>(g0) && run0 < static_cast<uint32_t>(g0 + kInplaceSlots)) {
+      uint32_t dest = run0;
+      for (int w = w_begin; w < w_end; ++w)
+        for (uint32_t rest = bitmap[w]; rest != 0u; rest &= rest - 1u, ++dest) {
+          const int s = static_cast<int>(dest) - g0;
+          if (s >= 0 && s < kInplaceSlots) src_pos[s] = w * 32 + __ffs(rest) - 1;
+        }
+    }
+    __syncthreads();
+    const int n_here = min(n_kept - g0, kInplaceSlots);
+    uint4 kreg[kPerThread], vreg[kPerThread];
+    bool move[kPerThread];
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = tid + i * kEvictThreads;
+      const int s = u / VEC, v = u % VEC;
+      move[i] = s < n_here && src_pos[s] != g0 + s;
+      if (move[i]) {
+        const long long off = static_cast<long long>(src_pos[s]) * VEC + v;
+        kreg[i] = kc[off];  // plain loads: this kernel writes the tensor it reads
+        vreg[i] = vc[off];
+      }
+    }
+    __syncthreads();  // every source of the round is in registers before a slot of the round is overwritten
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      if (move[i]) {
+        const long long off = static_cast<long long>(g0) * VEC + tid + i * kEvictThreads;
+        kc[off] = kreg[i];
+        vc[off] = vreg[i];
+      }
+    }
+  }
+}
+
 int dev_of() {
   int dev = 0;
   cudaGetDevice(&dev);
@@ -186,10 +269,13 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
   const size_t row_bytes = static_cast<size_t>(a.head_dim) * 2;
   const size_t src_bytes = static_cast<size_t>(a.rows) * a.src_cache_len * row_bytes;
   const size_t dst_bytes = static_cast<size_t>(a.rows) * a.dst_cache_len * row_bytes;
-  // CTAs of one row read positions other CTAs of the row may already have overwritten: packing in place is refused
-  if (overlaps(a.k_src, src_bytes, a.k_dst, dst_bytes) || overlaps(a.v_src, src_bytes, a.v_dst, dst_bytes) ||
+  // In place: exactly the same caches as source and destination.  Any other overlap is refused: CTAs of the
+  // out-of-place kernel read positions other CTAs of the row may already have overwritten.
+  const bool in_place = a.k_dst == a.k_src && a.v_dst == a.v_src && a.dst_cache_len == a.src_cache_len &&
+                        !overlaps(a.k_src, src_bytes, a.v_src, src_bytes);
+  if (!in_place && (overlaps(a.k_src, src_bytes, a.k_dst, dst_bytes) || overlaps(a.v_src, src_bytes, a.v_dst, dst_bytes) ||
       overlaps(a.k_src, src_bytes, a.v_dst, dst_bytes) || overlaps(a.v_src, src_bytes, a.k_dst, dst_bytes) ||
-      overlaps(a.k_dst, dst_bytes, a.v_dst, dst_bytes))
+      overlaps(a.k_dst, dst_bytes, a.v_dst, dst_bytes)))
     return TB200_ERR_INVALID;
   const uintptr_t align = reinterpret_cast<uintptr_t>(a.k_src) | reinterpret_cast<uintptr_t>(a.v_src) |
                           reinterpret_cast<uintptr_t>(a.k_dst) | reinterpret_cast<uintptr_t>(a.v_dst);
@@ -212,6 +298,25 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
   p.src_pitch = static_cast<long long>(a.src_cache_len) * vec;
   p.dst_pitch = static_cast<long long>(a.dst_cache_len) * vec;
 
+  const size_t smem = static_cast<size_t>(words) * sizeof(uint32_t);
+  static bool attr_set[32] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 31]) {
+    if (cudaFuncSetAttribute(kv_compact_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess ||
+        cudaFuncSetAttribute(kv_compact_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess ||
+        cudaFuncSetAttribute(kv_compact_inplace_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess ||
+        cudaFuncSetAttribute(kv_compact_inplace_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess)
+      return TB200_ERR_CUDA;
+    attr_set[dev & 31] = true;
+  }
+  if (in_place) {
+    p.groups = 0;
+    if (vec == 16) kv_compact_inplace_kernel<16><<<static_cast<unsigned>(a.rows), kEvictThreads, smem, stream>>>(p);
+    else kv_compact_inplace_kernel<8><<<static_cast<unsigned>(a.rows), kEvictThreads, smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  }
+
   // groups per CTA: the preamble costs about as much as one group per 2048 indices, so take two groups per 2048
   // indices (measured best on a B200: 2 up to 4096 indices, 4 at 8192), but leave at least four CTAs per SM
   int num_sms = 148;
@@ -225,16 +330,6 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
   if (const char* e = getenv("TB200_EVICT_GROUPS")) groups = atoi(e) < 1 ? 1 : (atoi(e) > kEvictMaxGroups ? kEvictMaxGroups : atoi(e));
   p.groups = static_cast<int>(groups);
   const dim3 grid(static_cast<unsigned>((groups_per_row + groups - 1) / groups), static_cast<unsigned>(a.rows));
-  const size_t smem = static_cast<size_t>(words) * sizeof(uint32_t);
-  static bool attr_set[32] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(kv_compact_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess ||
-        cudaFuncSetAttribute(kv_compact_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kEvictMaxWords * 4) != cudaSuccess)
-      return TB200_ERR_CUDA;
-    attr_set[dev & 31] = true;
-  }
   if (vec == 16) kv_compact_kernel<16><<<grid, kEvictThreads, smem, stream>>>(p);
   else kv_compact_kernel<8><<<grid, kEvictThreads, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;

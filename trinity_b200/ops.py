@@ -163,7 +163,7 @@ def kv_compact(k_src: torch.Tensor, v_src: torch.Tensor, idx: torch.Tensor, kv_l
 
     ``k_src, v_src``: ``(..., L, D)`` caches, leading axes = batch and kv heads; ``idx``: int32 ``(..., n_idx)`` over the
     same leading axes.  Returns ``(k_dst, v_dst, kept_pos, new_len)``; destination caches are allocated
-    ``(..., max_keep, D)`` when not given."""
+    ``(..., max_keep, D)`` when not given; ``k_dst=k_src, v_dst=v_src`` packs in place."""
     lib = L.load()
     if idx.dtype != torch.int32:
         raise TypeError("idx must be int32")
