@@ -108,7 +108,7 @@ ATTN_CLASSES = ["Vanilla", "PreNorm", "KeyFormer", "NormKeyFormer", "QKNorm", "N
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of youngchan2/Trinity")
     args = ap.parse_args()
     ref_rms, ffn_ref = load_reference(args.ref)
     torch.set_num_threads(os.cpu_count())

@@ -71,7 +71,7 @@ def check_all(ref_root, reference_generator):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of youngchan2/Trinity")
     ap.add_argument("--per-family", type=int, default=4)
     ap.add_argument("--check-all", action="store_true",
                     help="compare the replacement generator with the reference's on every stored candidate instead of writing fixtures")

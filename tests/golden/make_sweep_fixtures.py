@@ -31,7 +31,7 @@ CONFIGS = {"llama": {"M": 16, "D": 8, "N": 64, "P": 48, "H": 8}, "falcon": {"M":
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of youngchan2/Trinity")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     sys.path.insert(0, os.path.join(args.ref, "codegen"))  # the generator imports its siblings by bare name
