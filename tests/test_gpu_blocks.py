@@ -38,6 +38,13 @@ def check_common(got, ref, P):
     (1, 200, 256, 2, 2, 128, 56, Pn, {}),                        # PreNorm reference point (no weight)
     (1, 130, 256, 2, 2, 128, 0, Q, {}),                          # QKNorm reference point
     (3, 129, 264, 3, 3, 64, 255, C | Q, dict(weights=True, cache_extra=40)),
+    # decode-sized query blocks (key range dealt out over several CTAs, shares merged by attn_combine_kernel)
+    (2, 16, 512, 8, 2, 128, 1000, C, {}),                        # GQA, causal on a long cache, ragged last tile
+    (1, 5, 256, 4, 4, 64, 63, C, dict(dt=torch.float16)),        # 5 tokens, the diagonal crosses a tile boundary
+    (1, 16, 256, 4, 1, 64, 3, C | Pn | Q, dict(weights=True)),   # MQA, nearly empty cache, all norms
+    (1, 1, 256, 2, 2, 128, 777, 0, dict(cache_extra=9)),         # one token, many shares
+    (40, 3, 256, 16, 4, 128, 70, C, {}),                         # 640 heads in flight: one share per head, no merge
+    (2, 9, 512, 4, 2, 128, 0, C, {}),                            # no cache at all
 ])
 def test_attention_variants(B, S, N, Hq, Hkv, D, P, flags, kw):
     got, ref = attention_case(B, S, N, Hq, Hkv, D, P, flags, **kw)
@@ -52,6 +59,7 @@ def test_attention_variants(B, S, N, Hq, Hkv, D, P, flags, kw):
     (1, 16, 256, 2, 2, 128, 240, KF, dict(tau=1.5, topk=32)),
     (1, 140, 256, 2, 2, 128, 20, C | KF | Q, dict(tau=1.0, topk=16, aux_dtype=torch.bfloat16)),
     (1, 131, 256, 2, 2, 64, 5, KF, dict(tau=1.5)),               # past+S not a multiple of 8
+    (2, 12, 256, 8, 2, 128, 500, C | RC, dict(topk=50)),         # RoCo on a decode-sized block: its row statistic comes out of the merge of the key shares
 ])
 def test_score_outputs_and_topk(B, S, N, Hq, Hkv, D, P, flags, kw):
     got, ref = attention_case(B, S, N, Hq, Hkv, D, P, flags, **kw)
