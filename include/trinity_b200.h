@@ -199,7 +199,7 @@ int tb200_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, vo
  * after the other: n_idx = group * k) - a position any of them names is kept.  Bit-exact, no
  * workspace.  In place: pass k_dst == k_src, v_dst == v_src and dst_cache_len == src_cache_len
  * (one CTA per row packs front to back); any other overlap of source and destination is refused.
- * head_dim 64 or 128, 16-bit elements, kv_len <= 262144, rows <= 65535,
+ * head_dim 64 or 128, 16-bit elements, kv_len <= 262144, rows <= 65535 (out of place),
  * dst_cache_len >= tb200_kv_compact_max_keep(). */
 typedef struct {
   int dtype;                 /* TB200_F16 or TB200_BF16 (only the element size matters) */

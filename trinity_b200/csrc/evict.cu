@@ -263,7 +263,6 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
     return TB200_OK;
   }
   if (!a.k_src || !a.v_src || !a.k_dst || !a.v_dst || (a.n_idx > 0 && !a.idx)) return TB200_ERR_INVALID;
-  if (a.rows > 65535) return TB200_ERR_UNSUPPORTED;
   const int words = (a.kv_len + 31) / 32;
   if (words > kEvictMaxWords) return TB200_ERR_UNSUPPORTED;
   const size_t row_bytes = static_cast<size_t>(a.head_dim) * 2;
@@ -310,7 +309,7 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  if (in_place) {
+  if (in_place) {  // one CTA per row along grid.x: no limit on the number of rows
     p.groups = 0;
     if (vec == 16) kv_compact_inplace_kernel<16><<<static_cast<unsigned>(a.rows), kEvictThreads, smem, stream>>>(p);
     else kv_compact_inplace_kernel<8><<<static_cast<unsigned>(a.rows), kEvictThreads, smem, stream>>>(p);
@@ -327,8 +326,10 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
   groups = groups < 2 ? 2 : groups;
   groups = groups > fill ? fill : groups;
   groups = groups < 1 ? 1 : (groups > kEvictMaxGroups ? kEvictMaxGroups : groups);
-  if (const char* e = getenv("TB200_EVICT_GROUPS")) groups = atoi(e) < 1 ? 1 : (atoi(e) > kEvictMaxGroups ? kEvictMaxGroups : atoi(e));
+  static const int forced = getenv("TB200_EVICT_GROUPS") ? atoi(getenv("TB200_EVICT_GROUPS")) : 0;  // A/B switch for measurements
+  if (forced > 0) groups = forced > kEvictMaxGroups ? kEvictMaxGroups : forced;
   p.groups = static_cast<int>(groups);
+  if (a.rows > 65535) return TB200_ERR_UNSUPPORTED;  // rows run along grid.y
   const dim3 grid(static_cast<unsigned>((groups_per_row + groups - 1) / groups), static_cast<unsigned>(a.rows));
   if (vec == 16) kv_compact_kernel<16><<<grid, kEvictThreads, smem, stream>>>(p);
   else kv_compact_kernel<8><<<grid, kEvictThreads, smem, stream>>>(p);
