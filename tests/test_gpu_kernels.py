@@ -221,3 +221,23 @@ def test_kv_compact_rejects_bad_arguments(ops):
     # nothing to keep: a call that launches nothing and reports zero lengths
     _, _, pos, n = ops.kv_compact(k, v, idx[:, :0].contiguous(), 64)
     assert pos.shape == (2, 0) and n.cpu().tolist() == [0, 0]
+
+
+def test_kv_compact_under_graph_replay(ops):
+    """With caller-provided outputs the call allocates nothing: it can be captured and replayed like the blocks are."""
+    k, v, idx = (t.to(dev()) for t in _evict_case((4, 8), 1040, 1040, 128, 256, 32, torch.bfloat16, seed=21))
+    want = ops.kv_compact(k, v, idx, 1040, 32)                      # also the call outside capture (sets kernel attributes)
+    outs = [torch.zeros_like(t) for t in want]
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            ops.kv_compact(k, v, idx, 1040, 32, k_dst=outs[0], v_dst=outs[1], kept_pos=outs[2], new_len=outs[3])
+        for _ in range(3):
+            graph.replay()
+    torch.cuda.synchronize()
+    ops.device_status()
+    n = want[3].long()
+    live = (torch.arange(want[2].shape[-1], device=dev()).expand_as(want[2]) < n.unsqueeze(-1))
+    assert torch.equal(outs[3], want[3]) and torch.equal(outs[2], want[2])
+    assert torch.equal(outs[0][live], want[0][live]) and torch.equal(outs[1][live], want[1][live])
