@@ -47,6 +47,8 @@ def _free_port():
 def _ffn_worker(rank, world, port, case, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    chunks = {"plain3": 3, "tail5": 5}.get(case)       # down projection and all-reduce pipelined over row blocks
+    case = case.rstrip("35")
     try:
         t = orc.ref_ffn_inputs(12, 64, 96, seed=5, std=0.3)
         gelu = case == "gelu"
@@ -57,14 +59,15 @@ def _ffn_worker(rank, world, port, case, ret):
             n = t["O2"].shape[1] // world
             o2_local = t["O2"][:, rank * n:(rank + 1) * n].contiguous()
         out = shard.tensor_parallel_ffn(t["X"], sh, act="gelu" if gelu else "swiglu", o2_local=o2_local,
-                                        norm=case in ("block", "tail"), falcon_tail=case == "tail", local_ops=Fp32Ops())
+                                        norm=case in ("block", "tail"), falcon_tail=case == "tail", local_ops=Fp32Ops(),
+                                        overlap_chunks=chunks)
         if rank == 0:
             ret.put({k: v.clone() for k, v in out.items()})
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", ["plain", "gelu", "block", "tail"])
+@pytest.mark.parametrize("case", ["plain", "gelu", "block", "tail", "plain3", "tail5"])
 def test_tensor_parallel_ffn_two_ranks(case):
     ctx = mp.get_context("spawn")
     ret = ctx.SimpleQueue()
@@ -77,6 +80,7 @@ def test_tensor_parallel_ffn_two_ranks(case):
         p.join(60)
         assert p.exitcode == 0
     t = orc.ref_ffn_inputs(12, 64, 96, seed=5, std=0.3)
+    case = case.rstrip("35")
     if case == "plain":
         want = orc.ffn_block(t["X"], t["WFF1b"], t["WFF1a"], t["WFF2"])
         torch.testing.assert_close(got["FF2"], want["FF2"], rtol=1e-5, atol=1e-6)
