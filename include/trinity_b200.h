@@ -8,10 +8,15 @@
  * tensors are row-major and contiguous; `stream` is a cudaStream_t passed as void*.
  *
  * Conventions: return 0 (TB200_OK) or a negative tb200_status; never throw; never allocate device
- * memory, never synchronise the device (safe under CUDA-graph capture once the first call on a
- * device has run outside capture); workspace is supplied by the caller and sized by the
- * *_workspace_bytes() queries.  Argument checks (null, shape, 16-byte alignment) are done on the
- * host before anything is launched.
+ * memory (the only device state the library owns -- a 4-byte error word and the 16 MiB array of
+ * tb200_gemm_static_scratch -- are device symbols inside the library image); never synchronise the
+ * device, except tb200_device_status and tb200_attn_forward_timed, which say so.  The first call on a
+ * device looks up that device's properties and symbol addresses and must run outside stream capture;
+ * after it every entry point is safe under CUDA-graph capture.  Workspace is supplied by the caller and
+ * sized by the *_workspace_bytes() queries.  Argument checks (null, shape, 16-byte alignment of every
+ * tensor pointer, 4-byte alignment of the fp32 / int32 ones) are done on the host before anything is
+ * launched: a call that returns an error has launched nothing.  tb200_*_check() run those checks alone
+ * (no device needed).
  */
 #ifndef TRINITY_B200_H_
 #define TRINITY_B200_H_
@@ -39,8 +44,19 @@ const char* tb200_strerror(int status);
 /* Library/ABI version: major*1000 + minor. */
 int tb200_version(void);
 /* Reads (and clears) the device-side error word of the current device; 0 = no kernel gave up a wait.
+ * Every kernel of the library, tb200_gemm_static_scratch's included, reports there.
  * Synchronises the device -- a debugging / test aid, not part of the hot path. */
 int tb200_device_status(int* code_out);
+/* Every device-side wait (mbarrier, flag) is bounded: after this many SM cycles the waiting kernel records a
+ * code in the error word, lets all its roles leave their loops, frees its tensor memory and returns
+ * (TB200_ERR_DEVICE_TIMEOUT from tb200_device_status).  Default 4e9 (about 2 s); applies to launches made
+ * after the call; process-wide.  No counterpart in the reference (Triton kernels have no such waits). */
+int tb200_set_wait_limit_cycles(long long cycles);
+long long tb200_get_wait_limit_cycles(void);
+/* Test aid: launches a one-CTA kernel whose only mbarrier is never armed, with the given limit (1e3..2e9
+ * cycles), through the same bounded-wait code as the compute kernels.  The wait runs out, the kernel
+ * returns, and the next tb200_device_status reports TB200_ERR_DEVICE_TIMEOUT with code 900. */
+int tb200_selftest_wait_timeout(long long limit_cycles, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * RMSNorm: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) [* weight].
@@ -73,15 +89,17 @@ typedef struct {
 } tb200_gemm_args;
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
 int tb200_gemm(const tb200_gemm_args* args, void* stream);
+/* The host-side argument checks of tb200_gemm alone: nothing is launched, no device is needed. */
+int tb200_gemm_check(const tb200_gemm_args* args);
 /* No counterpart in the reference.  The same GEMM + epilogue as tb200_gemm, always computed as K slices
  * whose fp32 partial sums go into a 16 MiB array that is part of the library image, so that the call
- * performs NO device allocation at all (tb200_gemm's path creates a small per-device state with cudaMalloc
- * on its first call and takes a caller-allocated workspace).  Meant for hosts that are not allowed to
+ * performs NO device allocation at all (tb200_gemm takes a caller-allocated workspace for them).  Meant for hosts that are not allowed to
  * allocate: a server that gave all of HBM to its own pool, or code running under a foreign allocator.
  *   - args->workspace / workspace_bytes are ignored; split_k 0 lets the library choose.
  *   - split_k * m * n * 4 bytes (twice that with b2) must fit in 16 MiB, else TB200_ERR_SCRATCH_LIMIT.
- *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
- *     call before starting any stream capture.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, under a lock);
+ *     make that call before starting any stream capture.
+ *   - A bounded wait that runs out is reported through tb200_device_status, as for every other entry point.
  *   - All calls on a device share the one array: two calls that may run concurrently on the GPU (different
  *     streams) race on it.  Calls on one stream are ordered and safe.  Nothing in the array needs clearing
  *     between calls: every partial sum that is read has been written by the same call. */
@@ -103,7 +121,10 @@ enum {
   TB200_ATTN_QKNORM = 2,     /* per-head RMSNorm of q and k (normalised k is what is cached) */
   TB200_ATTN_CAUSAL = 4,     /* query i sees keys <= past + i */
   TB200_ATTN_KEYFORMER = 8,  /* c_out[b,h,j] = sum_i softmax_j((scale*s + noise)/tau)[i,j] */
-  TB200_ATTN_ROCO = 16       /* c_out1 = sum_i p[i,j], c_out2 = sum_i p[i,j]^2 */
+  TB200_ATTN_ROCO = 16,      /* c_out1 = sum_i p[i,j], c_out2 = sum_i p[i,j]^2 (what the reference's kernels emit) */
+  TB200_ATTN_ROCO_VARIANCE = 32 /* with ROCO: c_out2 = sum_i p^2 / n_j - (c_out1 / n_j)^2, the column variance over the n_j
+                                queries that can see key j (S, or S - max(0, j - past) under the causal mask); c_out1 stays
+                                the column sum, which is also what top-k ranks.  No counterpart in the reference. */
 };
 typedef struct {
   int dtype;                 /* TB200_F16 / TB200_BF16: x, weights, caches, o2, norm weights, noise */
@@ -136,6 +157,8 @@ typedef struct {
 } tb200_attn_args;
 size_t tb200_attn_workspace_bytes(const tb200_attn_args* args);
 int tb200_attn_forward(const tb200_attn_args* args, void* stream);
+/* The host-side argument checks of tb200_attn_forward alone (workspace excepted): nothing is launched. */
+int tb200_attn_check(const tb200_attn_args* args);
 /* Measuring aid with no counterpart in the reference (its harness times whole forward() calls,
  * benchmark/vanilla_llama_benchmark.py:277-294): the same block, with CUDA events recorded on `stream`
  * between its stages; waits for the stream and returns the stage durations in milliseconds:
@@ -176,6 +199,8 @@ typedef struct {
 } tb200_ffn_args;
 size_t tb200_ffn_workspace_bytes(const tb200_ffn_args* args);
 int tb200_ffn_forward(const tb200_ffn_args* args, void* stream);
+/* The host-side argument checks of tb200_ffn_forward alone (workspace excepted): nothing is launched. */
+int tb200_ffn_check(const tb200_ffn_args* args);
 
 /* ---------------------------------------------------------------------------------------------
  * Deterministic top-k over the last axis of scores (rows, n) fp32: idx[r,:] = the first k entries of

@@ -95,3 +95,72 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text, f"{f} mentions the oracle"
+
+
+# ---------------------------------------------------------------- host-side argument checks, no device, no launch
+def _gemm_args(**kw):
+    from trinity_b200 import _lib
+    base = dict(dtype=_lib.BF16, act=0, m=64, n=256, k=512, a=0x10000, b=0x20000, c=0x30000)
+    base.update(kw)
+    return _lib.GemmArgs(**base)
+
+
+def test_gemm_check_refuses_misaligned_pointers_on_the_host(lib):
+    """Every tensor pointer is touched with 16-byte accesses on some path (TMA, uint4 loads and stores of the K-slice
+    finish), so a misaligned one is refused by the host check -- with fake addresses, nothing is launched."""
+    assert lib.tb200_gemm_check(C.byref(_gemm_args())) == 0
+    for field in ("a", "b", "c"):
+        assert lib.tb200_gemm_check(C.byref(_gemm_args(**{field: 0x10008}))) == -1, field
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(b2=0x40004))) == -1
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(residual=0x40002))) == -1
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(row_scale=0x40002))) == -1
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(row_scale=0x40004))) == 0       # fp32: 4-byte alignment is enough
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(n=250))) == -1                   # n % 8
+    assert lib.tb200_gemm_check(C.byref(_gemm_args(c=None))) == -1
+    assert lib.tb200_gemm_check(None) == -1
+
+
+def _attn_args(**kw):
+    from trinity_b200 import _lib
+    base = dict(dtype=_lib.BF16, flags=0, batch=1, seq=16, hidden=512, n_q_heads=4, n_kv_heads=2, head_dim=128, past=0,
+                cache_len=16, sm_scale=1.0, tau=1.0, x=0x1000, wq=0x2000, wk=0x3000, wv=0x4000, k_cache=0x5000, v_cache=0x6000,
+                o2=0x7000, aux_dtype=_lib.F32)
+    base.update(kw)
+    return _lib.AttnArgs(**base)
+
+
+def test_attn_check_refuses_before_any_launch(lib):
+    from trinity_b200 import _lib
+    assert lib.tb200_attn_check(C.byref(_attn_args())) == 0
+    for field in ("x", "wq", "wk", "wv", "k_cache", "v_cache", "o2"):
+        assert lib.tb200_attn_check(C.byref(_attn_args(**{field: 0x1008}))) == -1, field
+    assert lib.tb200_attn_check(C.byref(_attn_args(flags=_lib.ATTN_PRENORM, norm_weight=0x8002))) == -1
+    # requests without a kernel are refused up front, not after the projection has already written the caches
+    both = _attn_args(flags=_lib.ATTN_KEYFORMER | _lib.ATTN_ROCO, noise=0x8000, c_out=0x9000, c_out1=0xa000, c_out2=0xb000)
+    assert lib.tb200_attn_check(C.byref(both)) == -2
+    long_topk = _attn_args(flags=_lib.ATTN_ROCO, seq=128, past=16384, cache_len=16512, c_out1=0xa000, c_out2=0xb000, topk=8, topk_idx=0xc000)
+    assert lib.tb200_attn_check(C.byref(long_topk)) == -2
+    assert lib.tb200_attn_check(C.byref(_attn_args(flags=_lib.ATTN_ROCO, c_out1=0xa002, c_out2=0xb000))) == -1
+    assert lib.tb200_attn_check(C.byref(_attn_args(flags=_lib.ATTN_ROCO_VARIANCE))) == -1   # variance without ROCO
+    assert lib.tb200_attn_check(C.byref(_attn_args(sm_scale=0.0))) == -1
+
+
+def test_ffn_check_refuses_misaligned_pointers(lib):
+    from trinity_b200 import _lib
+    base = dict(dtype=_lib.BF16, act=_lib.FFN_SWIGLU, flags=0, tokens=16, hidden=512, inner=1536, x=0x1000, w_gate=0x2000,
+                w_up=0x3000, w_down=0x4000, ff2=0x5000)
+    assert lib.tb200_ffn_check(C.byref(_lib.FfnArgs(**base))) == 0
+    for field in ("x", "w_gate", "w_up", "w_down", "ff2"):
+        bad = dict(base)
+        bad[field] = 0x1004
+        assert lib.tb200_ffn_check(C.byref(_lib.FfnArgs(**bad))) == -1, field
+    assert lib.tb200_ffn_check(C.byref(_lib.FfnArgs(**dict(base, ff1=0x6008)))) == -1
+    assert lib.tb200_ffn_check(C.byref(_lib.FfnArgs(**dict(base, w_up=None)))) == -1
+
+
+def test_wait_limit_is_a_host_setting(lib):
+    assert lib.tb200_get_wait_limit_cycles() == 4_000_000_000
+    assert lib.tb200_set_wait_limit_cycles(10) == -1                # refuses a limit no kernel could meet
+    assert lib.tb200_set_wait_limit_cycles(1_000_000) == 0
+    assert lib.tb200_get_wait_limit_cycles() == 1_000_000
+    assert lib.tb200_set_wait_limit_cycles(4_000_000_000) == 0

@@ -46,8 +46,12 @@ def test_attention_modules(text, kind, extra):
     assert m["KIND"] == kind and m["CONSTANTS"] == CONST
     import inspect
     sig = inspect.signature(m["forward"])
-    assert list(sig.parameters) == m["TENSOR_PARAMS"] + m["BLOCK_PARAMS"]
+    assert list(sig.parameters) == m["TENSOR_PARAMS"] + m["BLOCK_PARAMS"] + m["OPTIONAL_TENSOR_PARAMS"]
     assert all(sig.parameters[b].default == 16 for b in m["BLOCK_PARAMS"])
+    # tensors the reference's blocks do not have come last, keyword-only, default None: positional callers are unaffected
+    assert all(sig.parameters[o].kind is inspect.Parameter.KEYWORD_ONLY and sig.parameters[o].default is None
+               for o in m["OPTIONAL_TENSOR_PARAMS"])
+    assert m["OPTIONAL_TENSOR_PARAMS"] == {"vanilla": [], "prenorm": ["norm_weight"], "keyformer": ["topk_idx"], "roco": ["topk_idx"]}[kind]
 
 
 def test_cross_kernel_intermediate_becomes_a_parameter():

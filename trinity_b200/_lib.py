@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtrinity_b200.so")
 
 F16, BF16, F32 = 0, 1, 2
-ATTN_PRENORM, ATTN_QKNORM, ATTN_CAUSAL, ATTN_KEYFORMER, ATTN_ROCO = 1, 2, 4, 8, 16
+ATTN_PRENORM, ATTN_QKNORM, ATTN_CAUSAL, ATTN_KEYFORMER, ATTN_ROCO, ATTN_ROCO_VARIANCE = 1, 2, 4, 8, 16, 32
 FFN_SWIGLU, FFN_GELU = 0, 1
 FFN_NORM, FFN_FALCON_TAIL = 1, 2
 
@@ -66,6 +66,12 @@ SYMBOLS = {
     "tb200_strerror": (C.c_char_p, [C.c_int]),
     "tb200_version": (C.c_int, []),
     "tb200_device_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "tb200_set_wait_limit_cycles": (C.c_int, [C.c_longlong]),
+    "tb200_get_wait_limit_cycles": (C.c_longlong, []),
+    "tb200_selftest_wait_timeout": (C.c_int, [C.c_longlong, C.c_void_p]),
+    "tb200_gemm_check": (C.c_int, [C.POINTER(GemmArgs)]),
+    "tb200_attn_check": (C.c_int, [C.POINTER(AttnArgs)]),
+    "tb200_ffn_check": (C.c_int, [C.POINTER(FfnArgs)]),
     "tb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_int, C.c_void_p]),
     "tb200_gemm_workspace_bytes": (C.c_size_t, [C.POINTER(GemmArgs)]),
     "tb200_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),

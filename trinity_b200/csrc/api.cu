@@ -10,15 +10,16 @@ namespace tb200 {
 namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kTopkMaxKeys = 16384;   // launch_topk sorts one row in shared memory
 
 // How many K slices for a weight-streaming (few row-tiles) GEMM: as many as brings the number of work
 // units close to a whole number of waves over the SMs, at least 4 K-blocks per slice.
 int choose_split(int M, int n_tiles, int K, int num_sms) {
-  const int m_tiles = (M + kBM - 1) / kBM;
-  const int tiles = m_tiles * n_tiles;
+  const long long m_tiles = (M + kBM - 1) / kBM;
+  const long long tiles = m_tiles * n_tiles;   // 64-bit: the product of two tile counts can pass 2^31
   const int k_blocks = (K + kBK - 1) / kBK;
-  if (tiles * 2 > num_sms || k_blocks < 8) return 1;
-  int s = num_sms / tiles;
+  if (tiles < 1 || tiles * 2 > num_sms || k_blocks < 8) return 1;
+  int s = static_cast<int>(num_sms / tiles);
   if (s > k_blocks / 4) s = k_blocks / 4;
   if (s > 32) s = 32;
   return s < 1 ? 1 : s;
@@ -111,6 +112,9 @@ int check_gemm(const tb200_gemm_args* a) {
   if (a->m > (1 << 30) || a->n > (1 << 30) || a->k > (1 << 30)) return TB200_ERR_INVALID;
   if (!a->a || !a->b || !a->c) return TB200_ERR_INVALID;
   if (a->act != 0 && a->act != 1) return TB200_ERR_INVALID;
+  // every pointer a kernel touches with 16-byte accesses (TMA, uint4 loads and stores), whichever path is taken
+  if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->b2) || !aligned16(a->c) || !aligned16(a->residual)) return TB200_ERR_INVALID;
+  if (!aligned4(a->row_scale)) return TB200_ERR_INVALID;
   return TB200_OK;
 }
 
@@ -120,6 +124,8 @@ int check_gemm(const tb200_gemm_args* a) {
 using namespace tb200;
 
 extern "C" {
+
+int tb200_gemm_check(const tb200_gemm_args* a) { return check_gemm(a); }
 
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* a) {
   int status = TB200_OK;
@@ -157,12 +163,26 @@ static int check_attn(const tb200_attn_args* a) {
   if (!a->x || !a->wq || !a->wk || !a->wv || !a->k_cache || !a->v_cache || !a->o2) return TB200_ERR_INVALID;
   if ((a->flags & TB200_ATTN_KEYFORMER) && (!a->noise || !a->c_out || !(a->tau > 0.f))) return TB200_ERR_INVALID;
   if ((a->flags & TB200_ATTN_ROCO) && (!a->c_out1 || !a->c_out2)) return TB200_ERR_INVALID;
+  if ((a->flags & TB200_ATTN_ROCO_VARIANCE) && !(a->flags & TB200_ATTN_ROCO)) return TB200_ERR_INVALID;
   if ((a->flags & (TB200_ATTN_KEYFORMER | TB200_ATTN_ROCO)) && a->aux_dtype != TB200_F32 && a->aux_dtype != a->dtype)
     return TB200_ERR_INVALID;
   if (a->topk < 0 || a->topk > a->past + a->seq) return TB200_ERR_INVALID;
   if (a->topk > 0 && (!a->topk_idx || !(a->flags & (TB200_ATTN_KEYFORMER | TB200_ATTN_ROCO)))) return TB200_ERR_INVALID;
+  // requests no kernel exists for are refused here, before the first launch has touched the caches or o2
+  if ((a->flags & TB200_ATTN_KEYFORMER) && (a->flags & TB200_ATTN_ROCO)) return TB200_ERR_UNSUPPORTED;
+  if (a->topk > 0 && a->past + a->seq > kTopkMaxKeys) return TB200_ERR_UNSUPPORTED;
+  if (!(a->sm_scale > 0.f)) return TB200_ERR_INVALID;
+  const void* wide[] = {a->x, a->wq, a->wk, a->wv, a->k_cache, a->v_cache, a->o2, a->norm_weight, a->q_norm_weight,
+                        a->k_norm_weight, a->noise};
+  for (const void* ptr : wide)
+    if (!aligned16(ptr)) return TB200_ERR_INVALID;
+  const void* narrow[] = {a->c_out, a->c_out1, a->c_out2, a->topk_idx};
+  for (const void* ptr : narrow)
+    if (!aligned4(ptr)) return TB200_ERR_INVALID;
   return TB200_OK;
 }
+
+int tb200_attn_check(const tb200_attn_args* a) { return check_attn(a); }
 
 struct AttnWs {
   void* q;
@@ -319,7 +339,6 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
       return launch_score_colreduce(s, stream);
     };
     const float* topk_key = nullptr;
-    if (kf && rc) return TB200_ERR_UNSUPPORTED;  // one block is either KeyFormer or RoCo
     if (kf) {
       float* dst = stage ? w.sum_a : static_cast<float*>(a->c_out);
       if ((status = run_pass(true, nullptr, nullptr, dst)) != TB200_OK) return status;
@@ -329,6 +348,11 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
       float* d1 = stage ? w.sum_a : static_cast<float*>(a->c_out1);
       float* d2 = stage ? w.sum_b : static_cast<float*>(a->c_out2);
       if ((status = run_pass(false, d1, d2, nullptr)) != TB200_OK) return status;
+      if (a->flags & TB200_ATTN_ROCO_VARIANCE) {
+        status = launch_roco_variance(d1, d2, static_cast<int64_t>(a->batch) * a->n_q_heads, a->past + a->seq, a->past, a->seq,
+                                      (a->flags & TB200_ATTN_CAUSAL) ? 1 : 0, stream);
+        if (status != TB200_OK) return status;
+      }
       if (stage) {
         if ((status = launch_cast_f32(d1, a->c_out1, keys, a->aux_dtype, stream)) != TB200_OK) return status;
         if ((status = launch_cast_f32(d2, a->c_out2, keys, a->aux_dtype, stream)) != TB200_OK) return status;
@@ -372,8 +396,13 @@ static int check_ffn(const tb200_ffn_args* a) {
   if (a->act == TB200_FFN_SWIGLU && !a->w_up) return TB200_ERR_INVALID;
   if ((a->wo == nullptr) != (a->o2 == nullptr)) return TB200_ERR_INVALID;
   if ((a->flags & TB200_FFN_FALCON_TAIL) && !a->o_ff_norm) return TB200_ERR_INVALID;
+  const void* ptrs[] = {a->x, a->o2, a->wo, a->norm_weight, a->w_gate, a->w_up, a->w_down, a->ff2, a->attn_o2, a->ff1, a->o_ff_norm};
+  for (const void* ptr : ptrs)
+    if (!aligned16(ptr)) return TB200_ERR_INVALID;
   return TB200_OK;
 }
+
+int tb200_ffn_check(const tb200_ffn_args* a) { return check_ffn(a); }
 
 struct FfnWs {
   void* attn_o2;

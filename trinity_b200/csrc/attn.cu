@@ -61,6 +61,7 @@ struct AttnParams {
   const void* noise;
   float* lse2_perturbed;
   int* err;
+  long long wait_limit;  // cycles a bounded wait may last (tb200_set_wait_limit_cycles)
 };
 
 template <typename T, int D, bool NOISE>
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 2 * BKV;
-  const AbortCtx ctx{p.err, abort_flag};
+  const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -418,11 +419,9 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   if (!aligned16(a.q) || !aligned16(a.k_cache) || !aligned16(a.v_cache) || !aligned16(a.o2) || !aligned16(a.noise)) return TB200_ERR_INVALID;
   if (a.Hq > 65535 || a.B > 65535) return TB200_ERR_INVALID;
   if (!(a.sm_scale > 0.f)) return TB200_ERR_INVALID;  // the row maximum is taken before scaling
-  {  // the two-tile persistent kernel, except for a noise tensor whose rows are not 16-byte aligned (no TMA tiles)
-    static const bool single_tile = getenv("TB200_ATTN_SINGLE_TILE") != nullptr;  // A/B switch for measurements
-    if (!single_tile && a.noise == nullptr) return launch_attn_fwd_pingpong(a, stream);
-    if (!single_tile && ((a.past + a.S) & 7) == 0) return launch_attn_fwd_keyformer(a, stream);
-  }
+  // the two-tile persistent kernels, except for a noise tensor whose rows are not 16-byte aligned (no TMA tiles)
+  if (a.noise == nullptr) return launch_attn_fwd_pingpong(a, stream);
+  if (((a.past + a.S) & 7) == 0) return launch_attn_fwd_keyformer(a, stream);
 
   AttnParams p;
   memset(&p, 0, sizeof(p));
@@ -434,6 +433,7 @@ int launch_attn_fwd(const AttnLaunch& a, cudaStream_t stream) {
   p.noise = a.noise;
   p.lse2_perturbed = a.lse2_perturbed;
   p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};

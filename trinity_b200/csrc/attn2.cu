@@ -79,6 +79,7 @@ struct Attn2Params {
   float* part_o;     // (kv_splits, B, Hq, S, D) fp32, unnormalised
   float* part_ml;    // (kv_splits, B, Hq, S, 2): exponent reference and row sum of each part
   int* err;
+  long long wait_limit;  // cycles a bounded wait may last (tb200_set_wait_limit_cycles)
 };
 
 // One unit of work.  Items are numbered so that the longest (the last queries of a causal sequence) come first and
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const AbortCtx ctx{p.err, abort_flag};
+  const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -528,7 +529,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 }
 
 template <typename T, int D>
-int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
+int launch_one(const Attn2Params& p, dim3 grid, int num_sms, cudaStream_t stream) {
   static bool attr_set[32] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -542,7 +543,7 @@ int launch_one(const Attn2Params& p, dim3 grid, cudaStream_t stream) {
   if (p.kv_splits > 1) {
     const long long rows = static_cast<long long>(p.B) * p.Hq * p.S;
     long long blocks = (rows * 32 + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > num_sms * 8) blocks = num_sms * 8;
     attn_combine_kernel<T, D><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.part_o, p.part_ml, static_cast<T*>(p.o2), p.lse2,
                                                                              p.kv_splits, p.B, p.Hq, p.S);
     if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
@@ -579,6 +580,7 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.part_o = a.part_o;
   p.part_ml = a.part_ml;
   p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
@@ -603,9 +605,9 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
   p.d_group = make_fastdiv(static_cast<uint32_t>(a.Hq / a.Hkv));
   const dim3 grid(static_cast<unsigned>(p.n_items < st->num_sms ? p.n_items : st->num_sms), 1, 1);  // persistent: one CTA per SM
   if (a.dtype == TB200_BF16) {
-    return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, stream) : launch_one<__nv_bfloat16, 64>(p, grid, stream);
+    return a.D == 128 ? launch_one<__nv_bfloat16, 128>(p, grid, st->num_sms, stream) : launch_one<__nv_bfloat16, 64>(p, grid, st->num_sms, stream);
   }
-  return a.D == 128 ? launch_one<__half, 128>(p, grid, stream) : launch_one<__half, 64>(p, grid, stream);
+  return a.D == 128 ? launch_one<__half, 128>(p, grid, st->num_sms, stream) : launch_one<__half, 64>(p, grid, st->num_sms, stream);
 }
 
 }  // namespace tb200

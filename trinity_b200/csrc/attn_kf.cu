@@ -95,6 +95,7 @@ struct Attn2Params {
   float* part_o;     // (kv_splits, B, Hq, S, D) fp32, unnormalised
   float* part_ml;    // (kv_splits, B, Hq, S, 2): exponent reference and row sum of each part
   int* err;
+  long long wait_limit;  // cycles a bounded wait may last (tb200_set_wait_limit_cycles)
 };
 
 // One unit of work.  Items are numbered so that the longest (the last queries of a causal sequence) come first and
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const AbortCtx ctx{p.err, abort_flag};
+  const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
   // tensor-memory column of S buffer b of query tile t; O_t follows the four (or two) S tiles at column 256
   auto s_col = [](int t, int b) -> uint32_t { return static_cast<uint32_t>(NB == 2 ? (t * 2 + b) * 64 : t * 128); };
   constexpr uint32_t kOCol = 256;
@@ -473,7 +474,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
             const long long t0 = clock64();
             while (!(armed = *noise_issued > static_cast<int>(pos))) {
               if (*ctx.flag) break;
-              if (clock64() - t0 > kWaitLimitCycles) {
+              if (clock64() - t0 > ctx.limit) {
                 *ctx.flag = 1;
                 atomicCAS(ctx.gerr, 0, 413);
                 break;
@@ -678,6 +679,7 @@ int launch_attn_fwd_keyformer(const AttnLaunch& a, cudaStream_t stream) {
   p.part_o = a.part_o;
   p.part_ml = a.part_ml;
   p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};

@@ -2,9 +2,10 @@
 // tcgen05 (TMEM allocation, UMMA issue/commit, TMEM loads/stores) and shared-memory / instruction
 // descriptors.  Everything is inline PTX; there is no library dependency.
 //
-// Every wait on an mbarrier is BOUNDED: after kWaitLimitCycles the waiter records an error code in
+// Every wait on an mbarrier is BOUNDED: after AbortCtx::limit cycles (a kernel parameter, set on the host
+// with tb200_set_wait_limit_cycles; default kDefaultWaitLimitCycles) the waiter records an error code in
 // global memory, raises the CTA-wide abort flag and returns false; callers leave their loops, the CTA
-// joins at its final barrier, frees its TMEM and exits.  The host entry points turn a non-zero error
+// joins at its final barrier, frees its TMEM and exits.  tb200_device_status turns a non-zero error
 // word into TB200_ERR_DEVICE_TIMEOUT.
 #pragma once
 
@@ -16,7 +17,7 @@
 
 namespace tb200 {
 
-constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz; no legitimate wait is longer than a few ms
+constexpr long long kDefaultWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz; no legitimate wait is longer than a few ms
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -62,6 +63,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct AbortCtx {
   int* gerr;            // global error word (0 = ok)
   volatile int* flag;   // CTA-wide abort flag in shared memory
+  long long limit;      // cycles after which a wait gives up
 };
 
 // Bounded wait.  Returns false if the wait was abandoned (timeout here or abort raised elsewhere).
@@ -70,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {  // each failed try has been suspended for up to kSuspendNs
     if (*ctx.flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > ctx.limit) {
       *ctx.flag = 1;
       atomicCAS(ctx.gerr, 0, code);
       return false;
@@ -230,7 +232,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   const long long t0 = clock64();
   while (!mbar_try_wait_cluster(bar, parity)) {
     if (*ctx.flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > ctx.limit) {
       *ctx.flag = 1;
       atomicCAS(ctx.gerr, 0, code);
       return false;

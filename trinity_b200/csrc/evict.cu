@@ -318,16 +318,16 @@ int launch_kv_compact(const tb200_kv_compact_args& a, cudaStream_t stream) {
 
   // groups per CTA: the preamble costs about as much as one group per 2048 indices, so take two groups per 2048
   // indices (measured best on a B200: 2 up to 4096 indices, 4 at 8192), but leave at least four CTAs per SM
-  int num_sms = 148;
-  cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev_of());
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  const int num_sms = st->num_sms;
   const long long groups_per_row = (max_keep + kEvictSlots - 1) / kEvictSlots;
   const long long fill = groups_per_row * a.rows / (4LL * num_sms);
   long long groups = (a.n_idx + 2047) / 2048;
   groups = groups < 2 ? 2 : groups;
   groups = groups > fill ? fill : groups;
   groups = groups < 1 ? 1 : (groups > kEvictMaxGroups ? kEvictMaxGroups : groups);
-  static const int forced = getenv("TB200_EVICT_GROUPS") ? atoi(getenv("TB200_EVICT_GROUPS")) : 0;  // A/B switch for measurements
-  if (forced > 0) groups = forced > kEvictMaxGroups ? kEvictMaxGroups : forced;
   p.groups = static_cast<int>(groups);
   if (a.rows > 65535) return TB200_ERR_UNSUPPORTED;  // rows run along grid.y
   const dim3 grid(static_cast<unsigned>((groups_per_row + groups - 1) / groups), static_cast<unsigned>(a.rows));

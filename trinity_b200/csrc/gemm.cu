@@ -6,8 +6,10 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16, accumulators in TMEM
 //               (two 256-column accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
 //   warps 2-5   epilogue: tcgen05.ld (thread = output row, 32 columns at a time) -> fused epilogue -> global
-// No cluster launch and no multicast: every CTA fetches its own operands; reuse comes from L2, for which
-// the tile order walks groups of row-tiles across all column tiles.
+// With at least one 256-row tile per pair of SMs the kernel is launched as clusters of two CTAs that share a
+// 256 x 256 tile (tcgen05.mma.cta_group::2, see PAIR below); otherwise CTAs work alone.  No load is multicast:
+// every CTA fetches its own operand boxes; reuse comes from L2, for which the tile order walks groups of
+// row-tiles across all column tiles.
 //
 // The four B boxes of a stage may come from different weight tensors:
 //   GEMM_STORE / GEMM_PARTIAL  one source, 256 consecutive columns
@@ -17,6 +19,8 @@
 //                              to the caches
 #include <stdlib.h>
 #include <string.h>
+
+#include <mutex>
 
 #include "common.cuh"
 #include "internal.h"
@@ -57,6 +61,7 @@ struct GemmParams {
   int kv_merged;      // GEMM_QKV with at most 128 columns each of Wk and Wv: one tile holds both (K in accumulator
                       // columns [0,128), V in [128,256)) instead of two tiles that are three quarters empty
   int* err;
+  long long wait_limit;  // cycles a bounded wait may last (tb200_set_wait_limit_cycles)
   // epilogue
   const float* row_scale;
   void* C;
@@ -184,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (PAIR) cluster_sync_all(); else __syncthreads();  // a pair's barriers must exist before its peer signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const AbortCtx ctx{p.err, abort_flag};
+  const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -581,14 +586,8 @@ int launch_typed(const GemmParams& p, int mode, int slots, cudaStream_t stream) 
 
 // Pairs halve the B bytes each SM stages (measured +1.3 .. +4 % on 16384-row projections); they pay off when
 // there is a 256-row tile for every pair of SMs, so decode-size M keeps single CTAs.
-// TB200_GEMM_PAIR=0/1 forces the choice for every M >= 256 (read once).
 bool use_pair(int M, long long pair_units, int num_sms) {
-  static const int forced = [] {
-    const char* e = getenv("TB200_GEMM_PAIR");
-    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
-  }();
   if (M < 2 * BM) return false;
-  if (forced >= 0) return forced == 1;
   return pair_units >= num_sms / 2;
 }
 
@@ -656,6 +655,7 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   if (units > 0x7fffffffLL) return TB200_ERR_INVALID;
   p.total_units = static_cast<int>(units);
   p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
   p.row_scale = g.row_scale;
   p.C = g.C;
   p.ldc = g.ldc;
@@ -698,10 +698,17 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 
 int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
   if (f.M <= 0 || f.N <= 0 || (f.N & 7) != 0 || f.partial == nullptr || f.C == nullptr) return TB200_ERR_INVALID;
+  // the kernel moves 16 bytes at a time through every one of these
+  if (!aligned16(f.partial) || !aligned16(f.C) || !aligned16(f.C2) || !aligned16(f.residual) || (f.ldp & 3) != 0 || (f.ldc & 7) != 0 ||
+      (f.ldr & 7) != 0)
+    return TB200_ERR_INVALID;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
   const int64_t total = static_cast<int64_t>(f.M) * (f.N / 8);
   const int threads = 256;
   int64_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
   if (f.dtype == TB200_BF16) {
     splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
   } else if (f.dtype == TB200_F16) {
@@ -715,9 +722,13 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
 int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream) {
   if (f.M <= 0 || f.split_k < 1 || !f.partial || !f.q_out || !f.k_cache || !f.v_cache || (f.D != 64 && f.D != 128) || f.S <= 0)
     return TB200_ERR_INVALID;
+  if (!aligned16(f.partial) || !aligned16(f.q_out) || !aligned16(f.k_cache) || !aligned16(f.v_cache)) return TB200_ERR_INVALID;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
   const long long items = static_cast<long long>(f.M) * (f.Hq + 2 * f.Hkv);
   long long blocks = (items * 32 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
   const unsigned g = static_cast<unsigned>(blocks);
   if (f.dtype == TB200_BF16) {
     if (f.D == 128) qkv_finish_kernel<__nv_bfloat16, 128><<<g, 256, 0, stream>>>(f);
@@ -740,44 +751,29 @@ int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream) {
 // below instead of a caller- or library-allocated workspace.  Every GPU that loads the library carries
 // the array (kStaticScratchBytes) until the process exits.
 //
-// `g_static_scratch` and `g_static_err` are DEVICE symbols.  In host code their names are only handles:
-// the device addresses are fetched once per device with cudaGetSymbolAddress (that device current) and
-// it is those addresses that are passed to the kernels.
+// `g_static_scratch` is a DEVICE symbol.  In host code its name is only a handle: the device address is
+// fetched once per device with cudaGetSymbolAddress (that device current) and it is that address that is
+// passed to the kernels.  Bounded-wait expiries of this path are reported in the library's one error word
+// (tb200_device_status), like those of every other entry point.
 constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
-static __device__ int g_static_err;  // zero-initialised; the kernels' bounded waits report here
 
 namespace {
 
-struct StaticState {
-  bool ready = false;
-  int num_sms = 0;
-  float* scratch = nullptr;
-  int* err = nullptr;
-};
-StaticState g_static_state[32];
+std::mutex g_static_mu;
+float* g_static_ptr[32] = {};
 
-// First call on a device: resolve the symbols' device addresses.  Allocates nothing.
-int static_state(StaticState** out) {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 32) return TB200_ERR_CUDA;
-  StaticState& st = g_static_state[dev];
-  if (!st.ready) {
-    int major = 0;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return TB200_ERR_CUDA;
-    if (major != 10) return TB200_ERR_UNSUPPORTED;
-    if (cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TB200_ERR_CUDA;
+// First call on a device: resolve the symbol's device address (under a lock: two host threads may make their first
+// call at the same time).  Allocates nothing.
+int static_scratch_ptr(int dev, float** out) {
+  if (dev < 0 || dev >= 32) return TB200_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return TB200_ERR_CUDA;
-    st.scratch = static_cast<float*>(p);
-    p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_static_err) != cudaSuccess || p == nullptr) return TB200_ERR_CUDA;
-    st.err = static_cast<int*>(p);
-    int status = ensure_tensor_map_encoder();
-    if (status != TB200_OK) return status;
-    st.ready = true;
+    g_static_ptr[dev] = static_cast<float*>(p);
   }
-  *out = &st;
+  *out = g_static_ptr[dev];
   return TB200_OK;
 }
 
@@ -791,13 +787,18 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   if (!a->a || !a->b || !a->c || (a->act != 0 && a->act != 1) || a->split_k < 0) return TB200_ERR_INVALID;
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->b2) || !aligned16(a->c) || !aligned16(a->residual)) return TB200_ERR_INVALID;
   if (a->m == 0) return TB200_OK;
-  StaticState* st = nullptr;
-  int status = static_state(&st);
-  if (status != TB200_OK) return status;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);   // allocates nothing: SM count + the address of the error word
+  if (!st) return status;
+  float* scratch = nullptr;
+  if ((status = static_scratch_ptr(st->device, &scratch)) != TB200_OK) return status;
 
   const int M = static_cast<int>(a->m), N = static_cast<int>(a->n), K = static_cast<int>(a->k);
   const bool gated = a->b2 != nullptr;
   const int n_src = gated ? 2 : 1;
+  // even one slice must fit; checked in 64 bits before any tile arithmetic in int
+  const unsigned long long one_slice = static_cast<unsigned long long>(a->m) * n_src * static_cast<unsigned long long>(a->n) * sizeof(float);
+  if (one_slice > kStaticScratchBytes) return TB200_ERR_SCRATCH_LIMIT;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M;
@@ -806,9 +807,10 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   p.m_tiles = (M + BM - 1) / BM;
   p.group_m = p.m_tiles;  // decode-size M: one group
   p.n_tiles = n_src * ((N + BN - 1) / BN);
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;   // >= 1, bounded by the 16 MiB check above
   int split = a->split_k;
   if (split == 0) {  // as many slices as fill the SMs once, at least four K blocks each
-    split = st->num_sms / (p.m_tiles * p.n_tiles);
+    split = static_cast<int>(st->num_sms / tiles);
     if (split > p.k_blocks / 4) split = p.k_blocks / 4;
     if (split > 32) split = 32;
     if (split < 1) split = 1;
@@ -816,8 +818,7 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   if (split > p.k_blocks) split = p.k_blocks;
   p.kb_per_split = (p.k_blocks + split - 1) / split;
   p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
-  const size_t need = static_cast<size_t>(p.split_k) * M * n_src * N * sizeof(float);
-  if (need > kStaticScratchBytes) return TB200_ERR_SCRATCH_LIMIT;
+  if (one_slice * static_cast<unsigned long long>(p.split_k) > kStaticScratchBytes) return TB200_ERR_SCRATCH_LIMIT;
   p.n_src = n_src;
   p.tile_n = BN;
   for (int s = 0; s < n_src; ++s) {
@@ -825,9 +826,10 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
     p.src_tile0[s] = s * ((N + BN - 1) / BN);
   }
   for (int s = n_src; s < 4; ++s) p.src_tile0[s] = p.n_tiles;
-  p.total_units = p.m_tiles * p.n_tiles * p.split_k;
-  p.err = st->err;
-  p.partial = st->scratch;
+  p.total_units = static_cast<int>(tiles) * p.split_k;
+  p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
+  p.partial = scratch;
   p.ldp = static_cast<long long>(n_src) * N;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -850,7 +852,7 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   f.M = M;
   f.N = N;
   f.split_k = p.split_k;
-  f.partial = st->scratch;
+  f.partial = scratch;
   f.ldp = p.ldp;
   f.gated = gated ? 1 : 0;
   f.act = a->act;

@@ -10,12 +10,13 @@
 
 namespace tb200 {
 
-// Per-device state created by the first call on that device (outside any stream capture):
-// the device error word, the SM count and opt-in shared-memory attributes of the kernels.
+// Per-device state created by the first call on that device (outside any stream capture): the SM count and
+// the device address of the error word.  Creating it allocates nothing: the error word is a device symbol
+// inside the library image, looked up with cudaGetSymbolAddress.
 struct DeviceState {
   int device = -1;
   int num_sms = 0;
-  int* err_word = nullptr;  // device memory, 4 bytes, zero when healthy
+  int* err_word = nullptr;  // device address of the 4-byte error word, zero when healthy
 };
 // Returns nullptr (and sets *status) if the state cannot be created.
 DeviceState* device_state(int* status);
@@ -26,9 +27,12 @@ DeviceState* device_state(int* status);
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box);
 
-int ensure_tensor_map_encoder();
+// Cycles after which a bounded device-side wait gives up (tb200_set_wait_limit_cycles); copied into the
+// parameters of every kernel launch.
+long long wait_limit_cycles();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---------------------------------------------------------------- rmsnorm.cu
@@ -158,6 +162,7 @@ int launch_score_colreduce(const ScoreLaunch& s, cudaStream_t stream);
 
 // ---------------------------------------------------------------- topk.cu / misc
 int launch_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, cudaStream_t stream);
+int launch_roco_variance(const float* sum_p, float* sum_p2, int64_t rows, int kv_len, int past, int S, int causal, cudaStream_t stream);
 int launch_cast_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t stream);
 
 // ---------------------------------------------------------------- evict.cu

@@ -1,15 +1,23 @@
 // Per-device state, tensor-map encoding and the status helpers of the C ABI.
+#include <atomic>
 #include <mutex>
 
+#include "common.cuh"
 #include "internal.h"
 
 namespace tb200 {
+
+// The device error word: a DEVICE symbol, one instance per GPU that loads the library.  In host code the name is only
+// a handle; its device address is looked up once per device (that device current) with cudaGetSymbolAddress and
+// handed to every kernel.  Being part of the library image it costs no allocation.
+static __device__ int g_err_word;
 
 namespace {
 constexpr int kMaxDevices = 32;
 DeviceState g_states[kMaxDevices];
 bool g_ready[kMaxDevices];
 std::mutex g_mu;
+std::atomic<long long> g_wait_limit{4000000000LL};   // = kDefaultWaitLimitCycles of common.cuh
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -37,10 +45,12 @@ DeviceState* device_state(int* status) {
     return nullptr;
   }
   st.num_sms = prop.multiProcessorCount;
-  if (cudaMalloc(&st.err_word, sizeof(int)) != cudaSuccess || cudaMemset(st.err_word, 0, sizeof(int)) != cudaSuccess) {
+  void* err = nullptr;
+  if (cudaGetSymbolAddress(&err, g_err_word) != cudaSuccess || err == nullptr) {
     *status = TB200_ERR_CUDA;
     return nullptr;
   }
+  st.err_word = static_cast<int*>(err);
   if (!g_encode) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -55,17 +65,25 @@ DeviceState* device_state(int* status) {
   return &st;
 }
 
-// Resolve cuTensorMapEncodeTiled without creating the per-device state (no device allocation).
-int ensure_tensor_map_encoder() {
-  std::lock_guard<std::mutex> lock(g_mu);
-  if (g_encode) return TB200_OK;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
-      qres != cudaDriverEntryPointSuccess)
-    return TB200_ERR_CUDA;
-  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-  return TB200_OK;
+long long wait_limit_cycles() { return g_wait_limit.load(std::memory_order_relaxed); }
+
+// A kernel whose only job is to run one bounded wait to its end: one CTA, one mbarrier that nothing ever arms.  It
+// goes through the same mbar_wait / AbortCtx code as the compute kernels: the wait gives up after `limit` cycles,
+// records `code` in the device error word, raises the CTA's abort flag, and the kernel returns normally.
+__global__ void wait_selftest_kernel(int* err, long long limit, int code, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const AbortCtx ctx{err, &abort_flag, limit};
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(&bar, 0, ctx, code);   // phase 0 never completes
+  __syncthreads();
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = (!ok && abort_flag) ? 1 : 0;
 }
 
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
@@ -116,6 +134,23 @@ int tb200_device_status(int* code_out) {
   if (code != 0) cudaMemset(st->err_word, 0, sizeof(int));
   if (code_out) *code_out = code;
   return code == 0 ? TB200_OK : TB200_ERR_DEVICE_TIMEOUT;
+}
+
+int tb200_set_wait_limit_cycles(long long cycles) {
+  if (cycles < 1000) return TB200_ERR_INVALID;
+  tb200::g_wait_limit.store(cycles, std::memory_order_relaxed);
+  return TB200_OK;
+}
+
+long long tb200_get_wait_limit_cycles(void) { return tb200::wait_limit_cycles(); }
+
+int tb200_selftest_wait_timeout(long long limit_cycles, void* stream) {
+  if (limit_cycles < 1000 || limit_cycles > 2000000000LL) return TB200_ERR_INVALID;   // at most about a second
+  int status = TB200_OK;
+  tb200::DeviceState* st = tb200::device_state(&status);
+  if (!st) return status;
+  tb200::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st->err_word, limit_cycles, 900, nullptr);
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -104,6 +104,7 @@ struct ScoreParams {
   float* sum_p2;
   float* sum_pt;
   int* err;
+  long long wait_limit;  // cycles a bounded wait may last (tb200_set_wait_limit_cycles)
 };
 
 // One unit of work: a tile of 128 keys of one (q head, batch element) and the query tiles that can see it.  Items are
@@ -212,7 +213,7 @@ score_kernel(const __grid_constant__ ScoreParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const AbortCtx ctx{p.err, abort_flag};
+  const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA: K tile of each item, Q tiles through the ring
@@ -398,7 +399,7 @@ score_kernel(const __grid_constant__ ScoreParams p) {
             const long long c0 = clock64();
             while (!(armed = *noise_issued > static_cast<int>(n))) {
               if (*ctx.flag) break;
-              if (clock64() - c0 > kWaitLimitCycles) {
+              if (clock64() - c0 > ctx.limit) {
                 *ctx.flag = 1;
                 atomicCAS(ctx.gerr, 0, 310);
                 break;
@@ -574,6 +575,7 @@ int launch_score_colreduce(const ScoreLaunch& a, cudaStream_t stream) {
   p.sum_p2 = a.sum_p2;
   p.sum_pt = a.sum_pt;
   p.err = st->err_word;
+  p.wait_limit = wait_limit_cycles();
   const uint64_t D = static_cast<uint64_t>(a.D);
   {
     const uint64_t dims[3] = {D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B) * a.Hq};
@@ -605,8 +607,7 @@ int launch_score_colreduce(const ScoreLaunch& a, cudaStream_t stream) {
   // Long items (many query tiles per key tile) amortise the start and end of a CTA, and the hardware's own scheduling
   // of one CTA per item balances them best; with short items the persistent walk wins (measured for RoCo: -4 % at
   // S = 2048, +1.5 % at 4096, +4.5 % at 8192; for KeyFormer -15 %, -9 %, -4 %).
-  bool persistent = noise || p.q_tiles <= 16;  // KeyFormer: one CTA per SM, nothing else hides a CTA's start and end
-  if (const char* e = getenv("TB200_SCORE_PERSIST")) persistent = e[0] == '1';  // A/B switch for measurements
+  const bool persistent = noise || p.q_tiles <= 16;  // KeyFormer: one CTA per SM, nothing else hides a CTA's start and end
   const dim3 grid(static_cast<unsigned>((persistent && p.n_items > slots) ? slots : p.n_items), 1, 1);
   if (a.dtype == TB200_BF16) return launch_t<__nv_bfloat16>(p, a.D, noise, grid, stream);
   return launch_t<__half>(p, a.D, noise, grid, stream);

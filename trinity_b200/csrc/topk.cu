@@ -52,7 +52,33 @@ __global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, 
     dst[i] = static_cast<T>(src[i]);
 }
 
+// RoCo column variance from the two per-key sums: var_j = sum_p2_j / n_j - (sum_p_j / n_j)^2, n_j = the number of
+// queries that can see key j (all S without a mask; S - max(0, j - past) with the causal one).  In place over sum_p2.
+__global__ void roco_variance_kernel(const float* __restrict__ sum_p, float* __restrict__ sum_p2, int64_t total, int kv_len,
+                                     int past, int S, int causal) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % kv_len);
+    const int hidden = causal ? max(0, j - past) : 0;
+    const float n = static_cast<float>(S - hidden);
+    const float mean = sum_p[i] / n;
+    sum_p2[i] = sum_p2[i] / n - mean * mean;
+  }
+}
+
 }  // namespace
+
+int launch_roco_variance(const float* sum_p, float* sum_p2, int64_t rows, int kv_len, int past, int S, int causal, cudaStream_t stream) {
+  if (!sum_p || !sum_p2 || rows < 0 || kv_len <= 0 || S <= 0 || past < 0) return TB200_ERR_INVALID;
+  if (rows == 0) return TB200_OK;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  const int64_t total = rows * kv_len;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > st->num_sms * 16) blocks = st->num_sms * 16;
+  roco_variance_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sum_p, sum_p2, total, kv_len, past, S, causal);
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
 
 int launch_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, cudaStream_t stream) {
   if (scores == nullptr || idx == nullptr || rows < 0 || n <= 0 || k <= 0 || k > n) return TB200_ERR_INVALID;
@@ -75,8 +101,11 @@ int launch_topk(const float* scores, int32_t* idx, int64_t rows, int n, int k, c
 int launch_cast_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t stream) {
   if (n == 0) return TB200_OK;
   if (!src || !dst) return TB200_ERR_INVALID;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
   int64_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > st->num_sms * 16) blocks = st->num_sms * 16;
   if (dtype == TB200_BF16) cast_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
   else if (dtype == TB200_F16) cast_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, static_cast<__half*>(dst), n);
   else return TB200_ERR_UNSUPPORTED;

@@ -38,22 +38,47 @@ def _stream() -> int:
 
 
 class Workspace:
-    """A grow-only device buffer per (device, tag); grown outside of graph capture by the first call."""
+    """Scratch buffers the operators hand to the C ABI, one per (device, tag, stream).
+
+    * A buffer only grows, and only outside CUDA-graph capture (the first call sizes it).
+    * A buffer that is outgrown is RETIRED, not freed: a CUDA graph captured earlier holds its device address, and
+      the caching allocator must not hand that memory to another tensor while the graph can still be replayed.
+      ``Workspace.release()`` drops the retired buffers once no such graph is left.
+    * Buffers are keyed by the stream the call runs on, so eager calls on two streams never share partial sums; the
+      memory is allocated on that stream, so the allocator's stream bookkeeping is right without ``record_stream``.
+    * A capture on a stream that has no buffer yet adopts the one a warm-up call sized on another stream (capture
+      cannot allocate).  The two streams then share it: do not run that warm-up stream while the graph replays.
+    """
 
     _bufs: Dict[tuple, torch.Tensor] = {}
+    _retired: list = []
 
     @classmethod
     def get(cls, device: torch.device, nbytes: int, tag: str = "default") -> Optional[torch.Tensor]:
         if nbytes == 0:
             return None
-        key = (device.index, tag)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        key = (index, tag, torch.cuda.current_stream(device).cuda_stream)
         buf = cls._bufs.get(key)
         if buf is None or buf.numel() < nbytes:
             if torch.cuda.is_current_stream_capturing():
+                for (i, t, _), other in cls._bufs.items():
+                    if i == index and t == tag and other.numel() >= nbytes:
+                        if buf is not None:
+                            cls._retired.append(buf)
+                        cls._bufs[key] = other
+                        return other
                 raise RuntimeError("workspace must be sized by one call outside CUDA-graph capture first")
+            if buf is not None:
+                cls._retired.append(buf)
             buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
             cls._bufs[key] = buf
         return buf
+
+    @classmethod
+    def release(cls) -> None:
+        """Free the buffers that were outgrown.  Call only when no CUDA graph captured before the growth is replayed again."""
+        cls._retired.clear()
 
 
 def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
