@@ -65,6 +65,13 @@ int tb200_selftest_wait_timeout(long long limit_cycles, void* stream);
  * y may be NULL (statistics only); inv_rms (fp32, one per row) may be NULL.  cols % 8 == 0. */
 int tb200_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
                   float eps, int dtype, void* stream);
+/* w_out[k, :] = w[k, :] * norm_weight[k] over a (k, n) projection weight: folds an RMSNorm weight into the
+ * projection that follows the norm, once per model load, because (x * r * g) @ W = r * (x @ (diag(g) W)).  With
+ * the folded weights and TB200_ATTN_NORM_FOLDED / TB200_FFN_NORM_FOLDED the weighted norm is what the weight-free
+ * one is in the reference optimizer's own rewrite (evaluation/prenorm/prenorm_falcon_benchmark579.py:86-88): a row
+ * statistic and a per-row scale in the projection's epilogue; no normalised copy of x is written.  n % 8 == 0;
+ * w_out may not alias w. */
+int tb200_fold_norm_weight(const void* w, const void* norm_weight, void* w_out, int64_t k, int64_t n, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Fused GEMM  C = epilogue(A[m,k] @ B[k,n]),  16-bit inputs, fp32 accumulation on tcgen05/TMEM.
@@ -122,6 +129,8 @@ enum {
   TB200_ATTN_CAUSAL = 4,     /* query i sees keys <= past + i */
   TB200_ATTN_KEYFORMER = 8,  /* c_out[b,h,j] = sum_i softmax_j((scale*s + noise)/tau)[i,j] */
   TB200_ATTN_ROCO = 16,      /* c_out1 = sum_i p[i,j], c_out2 = sum_i p[i,j]^2 (what the reference's kernels emit) */
+  TB200_ATTN_NORM_FOLDED = 64, /* with PRENORM: wq, wk, wv already carry the norm weight (tb200_fold_norm_weight);
+                                norm_weight is ignored, only the row statistic is computed before the projection */
   TB200_ATTN_ROCO_VARIANCE = 32 /* with ROCO: c_out2 = sum_i p^2 / n_j - (c_out1 / n_j)^2, the column variance over the n_j
                                 queries that can see key j (S, or S - max(0, j - past) under the causal mask); c_out1 stays
                                 the column sum, which is also what top-k ranks.  No counterpart in the reference. */
@@ -174,7 +183,9 @@ int tb200_attn_forward_timed(const tb200_attn_args* args, void* stream, float* s
 enum { TB200_FFN_SWIGLU = 0, TB200_FFN_GELU = 1 };
 enum {
   TB200_FFN_NORM = 1,        /* RMSNorm of a before the up projections */
-  TB200_FFN_FALCON_TAIL = 2  /* o_ff = ff2 + h, o_ff_norm = o_ff / sqrt(sum(o_ff^2)/tail_divisor) */
+  TB200_FFN_FALCON_TAIL = 2, /* o_ff = ff2 + h, o_ff_norm = o_ff / sqrt(sum(o_ff^2)/tail_divisor) */
+  TB200_FFN_NORM_FOLDED = 4  /* with NORM: w_gate (and w_up) already carry the norm weight (tb200_fold_norm_weight);
+                                not with FALCON_TAIL, whose residual is the normalised h itself */
 };
 typedef struct {
   int dtype;

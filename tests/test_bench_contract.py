@@ -30,12 +30,29 @@ def test_reference_arm_line():
     assert d["config"]["workload"] == "tiny" and "model" not in d["config"]
 
 
+@pytest.mark.parametrize("workload,metric", [("llama3_8b_swiglu_ffn_m64", "fused_block_tflops"), ("llama3_8b_vanilla_decode_m16_p1024", "fused_block_tflops"),
+                                             ("llama3_8b_kv_evict_b4_l4096_k1024", "kv_evict_gbs"), ("rmsnorm_32768x4096", "rmsnorm_gbs")])
+def test_reference_arm_covers_every_kind_of_workload(workload, metric):
+    d = run_bench("--impl", "reference", "--workload", workload, "--steps", "1", "--warmup", "0")
+    assert d["impl"] == "reference" and d["metric"] == metric and d["value"] > 0
+    assert d["config"]["workload"] == workload and d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["sample"]
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_both_arms_print_the_same_config():
+    sys.path.insert(0, ROOT)
+    import bench
+    for name, w in bench.WORKLOADS.items():
+        c = bench.workload_config(name, w)
+        assert c["workload"] == name and "model" not in c and "recorded_ms" not in c
+
+
 def test_workload_table():
     sys.path.insert(0, ROOT)
     import bench
     assert bench.DEFAULT in bench.WORKLOADS and bench.WORKLOADS[bench.DEFAULT].get("kind") is None
     kinds = {w.get("kind", "attention") for w in bench.WORKLOADS.values()}
-    assert kinds == {"attention", "ffn", "evict", "decode"}
+    assert kinds == {"attention", "ffn", "evict", "decode", "rmsnorm"}
     for name, w in bench.WORKLOADS.items():
         if w.get("kind") is None:
             assert w["Hq"] % w["Hkv"] == 0 and w["D"] in (64, 128) and w["N"] % 8 == 0, name
@@ -49,7 +66,8 @@ def test_workload_table():
 @pytest.mark.gpu
 def test_native_arm_line_on_the_smallest_workload():
     d = run_bench("--workload", "tiny", "--steps", "3", "--warmup", "3", "--no-cpu-baseline")
-    assert BASE_KEYS | {"roofline", "clocks", "gpu_launches"} <= set(d)
+    assert BASE_KEYS | {"roofline", "clocks", "gpu_launches", "timed_region_s", "burst", "passes_per_step"} <= set(d)
+    assert d["e2e"]["api"].startswith("generated-module forward(")
     assert d["gpu_launches"] > 0 and d["value"] > 0 and d["e2e"]["value"] > 0
     assert d["e2e"]["h2d_bytes_per_step"] > 0 and d["e2e"]["d2h_bytes_per_step"] > 0
     r = d["roofline"]

@@ -72,3 +72,49 @@ def test_graph_replay_survives_a_larger_eager_call():
     close(big, a2.float() @ b2.float(), msg="the larger call")
     assert all(bool(torch.isnan(j).all()) for j in junk), "the replay wrote into memory it no longer owns"
     assert ops.device_status() == 0
+
+
+def test_norm_weight_folded_into_the_projections():
+    """(x * r * g) @ W = r * (x @ (diag(g) W)): the block with the folded weights (the default through ops) and with the
+    materialised normalised activations agree with the oracle and with each other, and the folded path needs no room
+    for a normalised copy of x."""
+    import ctypes as C
+    from .gpu_util import attention_case
+    flags = L.ATTN_PRENORM | L.ATTN_CAUSAL
+    try:
+        ops.FoldedWeights.enabled = False
+        plain, ref = attention_case(2, 300, 1024, 8, 2, 128, 20, flags, weights=True, seed=9)
+        ops.FoldedWeights.enabled = True
+        ops.FoldedWeights.clear()
+        folded, _ = attention_case(2, 300, 1024, 8, 2, 128, 20, flags, weights=True, seed=9)
+    finally:
+        ops.FoldedWeights.enabled = True
+    close(plain["O2"], ref["O2"], msg="O2, materialised norm")
+    close(folded["O2"], ref["O2"], msg="O2, folded norm weight")
+    close(folded["K_new"], ref["K_new"], msg="appended K rows, folded norm weight")
+    close(folded["O2"], plain["O2"].float(), msg="folded against materialised")
+    lib = L.load()
+    a = L.AttnArgs(dtype=L.BF16, flags=flags, batch=2, seq=300, hidden=1024, n_q_heads=8, n_kv_heads=2, head_dim=128, past=20,
+                   cache_len=320, sm_scale=1.0, tau=1.0, x=0x1000, wq=0x2000, wk=0x3000, wv=0x4000, k_cache=0x5000, v_cache=0x6000,
+                   o2=0x7000, norm_weight=0x8000, aux_dtype=L.F32)
+    unfolded_bytes = lib.tb200_attn_workspace_bytes(C.byref(a))
+    a.flags = flags | L.ATTN_NORM_FOLDED
+    assert unfolded_bytes - lib.tb200_attn_workspace_bytes(C.byref(a)) >= 2 * 300 * 1024 * 2 - 4096   # x_norm is gone
+
+
+def test_ffn_block_with_a_weighted_norm():
+    """The reference FFN block with a norm weight and eps (extension; the reference's norm has neither), folded into
+    the gate / up projections."""
+    g = torch.Generator().manual_seed(21)
+    M, N, P = 200, 512, 1536
+    rn = lambda *s: torch.randn(*s, generator=g)
+    t = {"O2": rn(M, N), "X": rn(M, N), "WO": rn(N, N) * N ** -0.5, "WFF1a": rn(N, P) * N ** -0.5, "WFF1b": rn(N, P) * N ** -0.5,
+         "WFF2": rn(P, N) * P ** -0.5, "g": 1 + 0.1 * rn(N)}
+    t = {k: v.to(torch.bfloat16) for k, v in t.items()}
+    d = {k: v.to(dev()) for k, v in t.items()}
+    ff2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.ffn_forward(d["X"], d["WFF1b"], d["WFF1a"], d["WFF2"], ff2, flags=L.FFN_NORM, o2=d["O2"], wo=d["WO"], norm_weight=d["g"], norm_eps=1e-5)
+    ops.device_status()
+    f = lambda k: t[k].float()
+    ref = orc.ffn_block(f("O2"), f("WFF1b"), f("WFF1a"), f("WFF2"), wo=f("WO"), residual=f("X"), norm=True, norm_weight=f("g"), norm_eps=1e-5)
+    close(ff2, ref["FF2"], rtol=3e-2, atol=3e-2 * float(ref["FF2"].abs().max()), msg="FF2")

@@ -9,9 +9,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtrinity_b200.so")
 
 F16, BF16, F32 = 0, 1, 2
-ATTN_PRENORM, ATTN_QKNORM, ATTN_CAUSAL, ATTN_KEYFORMER, ATTN_ROCO, ATTN_ROCO_VARIANCE = 1, 2, 4, 8, 16, 32
+ATTN_PRENORM, ATTN_QKNORM, ATTN_CAUSAL, ATTN_KEYFORMER, ATTN_ROCO, ATTN_ROCO_VARIANCE, ATTN_NORM_FOLDED = 1, 2, 4, 8, 16, 32, 64
 FFN_SWIGLU, FFN_GELU = 0, 1
-FFN_NORM, FFN_FALCON_TAIL = 1, 2
+FFN_NORM, FFN_FALCON_TAIL, FFN_NORM_FOLDED = 1, 2, 4
 
 
 class GemmArgs(C.Structure):
@@ -73,6 +73,7 @@ SYMBOLS = {
     "tb200_attn_check": (C.c_int, [C.POINTER(AttnArgs)]),
     "tb200_ffn_check": (C.c_int, [C.POINTER(FfnArgs)]),
     "tb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_int, C.c_void_p]),
+    "tb200_fold_norm_weight": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "tb200_gemm_workspace_bytes": (C.c_size_t, [C.POINTER(GemmArgs)]),
     "tb200_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "tb200_gemm_static_scratch": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),

@@ -207,9 +207,11 @@ static AttnWs carve_attn(const tb200_attn_args* a, void* base, int num_sms) {
   const size_t keys = static_cast<size_t>(a->batch) * a->n_q_heads * (a->past + a->seq);
   const bool prenorm = a->flags & TB200_ATTN_PRENORM;
   const bool aux = a->flags & (TB200_ATTN_KEYFORMER | TB200_ATTN_ROCO);
+  // the normalised activations are only materialised for a norm weight that has not been folded into the projections
+  const bool materialise = prenorm && a->norm_weight && !(a->flags & TB200_ATTN_NORM_FOLDED);
   w.q = c.take(rows * a->head_dim * 2);
-  w.x_norm = (prenorm && a->norm_weight) ? c.take(T * a->hidden * 2) : nullptr;
-  w.inv_rms = (prenorm && !a->norm_weight) ? static_cast<float*>(c.take(T * 4)) : nullptr;
+  w.x_norm = materialise ? c.take(T * a->hidden * 2) : nullptr;
+  w.inv_rms = (prenorm && !materialise) ? static_cast<float*>(c.take(T * 4)) : nullptr;
   w.lse2 = static_cast<float*>(c.take(rows * 4));
   w.lse2t = (a->flags & TB200_ATTN_KEYFORMER) ? static_cast<float*>(c.take(rows * 4)) : nullptr;
   const bool stage = aux && a->aux_dtype != TB200_F32;
@@ -248,13 +250,14 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
   const int T = a->batch * a->seq;
   const int D = a->head_dim;
 
-  // 1. RMSNorm prologue: with a weight the normalised activations are materialised; without one only the
-  //    row statistic is computed and the scale is applied in the projection's epilogue.
+  // 1. RMSNorm prologue.  Without a weight, or with the weight folded into the rows of Wq, Wk, Wv
+  //    (TB200_ATTN_NORM_FOLDED), only the row statistic is computed and the scale is applied in the projection's
+  //    epilogue; with an unfolded weight the normalised activations are materialised.
   const void* A = a->x;
   const float* row_scale = nullptr;
   if (ev) cudaEventRecord(ev[0], stream);
   if (a->flags & TB200_ATTN_PRENORM) {
-    if (a->norm_weight) {
+    if (w.x_norm) {
       status = launch_rmsnorm(a->x, a->norm_weight, w.x_norm, nullptr, T, a->hidden, a->norm_eps, a->dtype, stream);
       A = w.x_norm;
     } else {
@@ -396,6 +399,7 @@ static int check_ffn(const tb200_ffn_args* a) {
   if (a->act == TB200_FFN_SWIGLU && !a->w_up) return TB200_ERR_INVALID;
   if ((a->wo == nullptr) != (a->o2 == nullptr)) return TB200_ERR_INVALID;
   if ((a->flags & TB200_FFN_FALCON_TAIL) && !a->o_ff_norm) return TB200_ERR_INVALID;
+  if ((a->flags & TB200_FFN_NORM_FOLDED) && (a->flags & TB200_FFN_FALCON_TAIL)) return TB200_ERR_UNSUPPORTED;  // the tail adds h itself
   const void* ptrs[] = {a->x, a->o2, a->wo, a->norm_weight, a->w_gate, a->w_up, a->w_down, a->ff2, a->attn_o2, a->ff1, a->o_ff_norm};
   for (const void* ptr : ptrs)
     if (!aligned16(ptr)) return TB200_ERR_INVALID;
@@ -421,8 +425,10 @@ static FfnWs carve_ffn(const tb200_ffn_args* a, void* base, int num_sms) {
   const bool norm = a->flags & TB200_FFN_NORM, tail = a->flags & TB200_FFN_FALCON_TAIL;
   const bool gated = a->act == TB200_FFN_SWIGLU;
   w.attn_o2 = (a->wo && !a->attn_o2) ? c.take(M * N * 2) : a->attn_o2;
-  // h is materialised when the norm has a weight or when the tail needs it as a residual
-  w.h = (norm && (a->norm_weight || tail)) ? c.take(M * N * 2) : nullptr;
+  // h is materialised when the norm has a weight that is not folded into w_gate / w_up, or when the tail needs it as
+  // a residual
+  const bool folded = a->flags & TB200_FFN_NORM_FOLDED;
+  w.h = (norm && ((a->norm_weight && !folded) || tail)) ? c.take(M * N * 2) : nullptr;
   w.inv_rms = (norm && !w.h) ? static_cast<float*>(c.take(M * 4)) : nullptr;
   w.ff1 = a->ff1 ? a->ff1 : c.take(M * P * 2);
   w.o_ff = tail ? c.take(M * N * 2) : nullptr;

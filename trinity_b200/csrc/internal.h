@@ -41,6 +41,8 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
                    float eps, int dtype, cudaStream_t stream, int mean_divisor = 0);
 
+int launch_fold_rows(const void* w, const void* g, void* out, int64_t k, int64_t n, int dtype, cudaStream_t stream);
+
 // ---------------------------------------------------------------- gemm.cu
 enum GemmMode {
   GEMM_STORE = 0,    // c = act(acc * row_scale) + residual

@@ -87,7 +87,47 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const T* __restrict__
   for (int v = threadIdx.x + kCachedVecs * kThreads; v < nvec; v += kThreads) scale_store(v, __ldg(xr + v));
 }
 
+// out[k, :] = w[k, :] * g[k]: the norm weight folded into the rows of a (K, N) projection weight, so that
+// (x * r * g) @ W = r * (x @ (diag(g) W)) and the weighted norm costs the projection nothing but its row scale.
+template <typename T>
+__global__ void fold_rows_kernel(const T* __restrict__ w, const T* __restrict__ g, T* __restrict__ out, int64_t k, int64_t nvec) {
+  const int64_t total = k * nvec;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / nvec;
+    const float gr = static_cast<float>(g[row]);
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(w) + i);
+    const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = Pack2<T>::unpack(in[j]);
+      o[j] = Pack2<T>::pack(f.x * gr, f.y * gr);
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace
+
+int launch_fold_rows(const void* w, const void* g, void* out, int64_t k, int64_t n, int dtype, cudaStream_t stream) {
+  if (!w || !g || !out || k <= 0 || n <= 0 || (n & 7) != 0 || k > (1 << 30) || n > (1 << 30)) return TB200_ERR_INVALID;
+  if (!aligned16(w) || !aligned16(out) || (reinterpret_cast<uintptr_t>(g) & 1) != 0) return TB200_ERR_INVALID;
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  const int64_t nvec = n / 8;
+  int64_t blocks = (k * nvec + 255) / 256;
+  if (blocks > st->num_sms * 16) blocks = st->num_sms * 16;
+  if (dtype == TB200_BF16)
+    fold_rows_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(g),
+                                                                                    static_cast<__nv_bfloat16*>(out), k, nvec);
+  else if (dtype == TB200_F16)
+    fold_rows_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __half*>(w), static_cast<const __half*>(g),
+                                                                             static_cast<__half*>(out), k, nvec);
+  else
+    return TB200_ERR_UNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+}
 
 int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols, float eps,
                    int dtype, cudaStream_t stream, int mean_divisor) {
@@ -111,6 +151,10 @@ int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, i
 }
 
 }  // namespace tb200
+
+extern "C" int tb200_fold_norm_weight(const void* w, const void* norm_weight, void* w_out, int64_t k, int64_t n, int dtype, void* stream) {
+  return tb200::launch_fold_rows(w, norm_weight, w_out, k, n, dtype, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int tb200_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t cols,
                              float eps, int dtype, void* stream) {

@@ -81,6 +81,45 @@ class Workspace:
         cls._retired.clear()
 
 
+class FoldedWeights:
+    """Projection weights with an RMSNorm weight folded into their rows (``tb200_fold_norm_weight``), kept per set of
+    source tensors.  ``(x * r * g) @ W = r * (x @ (diag(g) W))``: with the folded copy the weighted norm in front of a
+    projection is a row statistic and a per-row scale in the projection's epilogue, no normalised copy of ``x``.
+
+    A folded copy is made at the first call that sees a (weights, norm weight) combination -- outside CUDA-graph
+    capture, like any one-time set-up; under capture an unseen combination runs the unfolded path -- and reused while
+    the source tensors are alive and unmodified (their torch version counters are part of the key).  It costs the
+    projection's weight bytes once more in HBM; ``FoldedWeights.enabled = False`` turns folding off."""
+
+    enabled = True
+    _cache: Dict[tuple, tuple] = {}
+
+    @classmethod
+    def get(cls, g: torch.Tensor, *weights: torch.Tensor):
+        if not cls.enabled:
+            return None
+        key = (g.data_ptr(), g._version) + tuple((w.data_ptr(), w._version, tuple(w.shape)) for w in weights)
+        hit = cls._cache.get(key)
+        if hit is not None:
+            return hit[0]
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        lib = L.load()
+        folded = []
+        for w in weights:
+            out = torch.empty_like(w)
+            L.check(lib.tb200_fold_norm_weight(_ptr(w), _ptr(g), _ptr(out), w.shape[0], w.shape[1], _dt(w), _stream()), "tb200_fold_norm_weight")
+            folded.append(out)
+        if len(cls._cache) >= 64:          # a bound, not a policy: drop the oldest entry
+            cls._cache.pop(next(iter(cls._cache)))
+        cls._cache[key] = (tuple(folded), (g,) + weights)   # the sources are kept alive so that their addresses stay theirs
+        return tuple(folded)
+
+    @classmethod
+    def clear(cls) -> None:
+        cls._cache.clear()
+
+
 def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
             out: Optional[torch.Tensor] = None, inv_rms: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = L.load()
@@ -133,6 +172,11 @@ def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: in
     n_q = wq.shape[1] // head_dim
     n_kv = wk.shape[1] // head_dim
     cache_len = k_cache.shape[-2]
+    if (flags & L.ATTN_PRENORM) and norm_weight is not None and not (flags & L.ATTN_NORM_FOLDED):
+        folded = FoldedWeights.get(norm_weight, wq, wk, wv)
+        if folded is not None:
+            wq, wk, wv = folded
+            flags |= L.ATTN_NORM_FOLDED
     aux = c_out if c_out is not None else c_out1
     args = L.AttnArgs(
         dtype=_dt(x), flags=flags, batch=batch, seq=seq, hidden=hidden, n_q_heads=n_q, n_kv_heads=n_kv,
@@ -161,6 +205,11 @@ def ffn_forward(x, w_gate, w_up, w_down, ff2, *, act: int = L.FFN_SWIGLU, flags:
     hidden = x.shape[-1]
     tokens = x.numel() // hidden
     inner = w_gate.shape[1]
+    if (flags & L.FFN_NORM) and norm_weight is not None and not (flags & (L.FFN_NORM_FOLDED | L.FFN_FALCON_TAIL)):
+        folded = FoldedWeights.get(norm_weight, *([w_gate] if w_up is None else [w_gate, w_up]))
+        if folded is not None:
+            w_gate, w_up = folded[0], (folded[1] if w_up is not None else None)
+            flags |= L.FFN_NORM_FOLDED
     args = L.FfnArgs(dtype=_dt(x), act=act, flags=flags, tokens=tokens, hidden=hidden, inner=inner, norm_eps=norm_eps,
                      tail_divisor=tail_divisor, x=_ptr(x), o2=_ptr(o2), wo=_ptr(wo), norm_weight=_ptr(norm_weight),
                      w_gate=_ptr(w_gate), w_up=_ptr(w_up), w_down=_ptr(w_down), ff2=_ptr(ff2), attn_o2=_ptr(attn_o2),
