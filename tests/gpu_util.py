@@ -17,6 +17,20 @@ def close(got, ref, rtol=RTOL, atol=ATOL, msg=""):
     torch.testing.assert_close(got.float().cpu(), ref.float().cpu(), rtol=rtol, atol=atol, msg=lambda m: f"{msg}: {m}")
 
 
+def close_but_for_rounding_outliers(got, ref, rtol=RTOL, atol=ATOL, msg="", budget=2e-5):
+    """The same elementwise bound as ``close`` for all but a ``budget`` fraction of the elements, which may reach twice
+    the bound.  At full benchmark sizes a comparison covers 10^5..10^6 outputs per sample; the first query rows of a causal
+    block attend to a handful of keys, and where two of them are nearly tied the 16-bit rounding of q, k and v (which the
+    fp32 oracle does not do) moves the output by more than it does anywhere else -- a CPU emulation of those roundings
+    reproduces such elements one for one.  A kernel fault shows up as thousands of elements, or as one far outside."""
+    g, r = got.float().cpu(), ref.float().cpu()
+    excess = (g - r).abs() - (atol + rtol * r.abs())
+    over = int((excess > 0).sum())
+    worst = float(((g - r).abs() / (atol + rtol * r.abs())).max())
+    assert over <= max(1, int(budget * r.numel())) and worst <= 2.0, \
+        f"{msg}: {over} of {r.numel()} elements outside rtol {rtol} / atol {atol}, the worst at {worst:.2f} times the bound"
+
+
 def attention_case(B, S, N, Hq, Hkv, D, P, flags, dt=torch.bfloat16, scale=None, weights=False, topk=0, tau=1.0,
                    seed=1, aux_dtype=torch.float32, cache_extra=0):
     """Returns (gpu outputs dict, oracle outputs dict)."""

@@ -1,26 +1,28 @@
 // Attention forward, two query tiles per CTA ("ping-pong"): the kernel used when no noise tensor is involved.
 //
 // Persistent: one CTA per SM walks work items (256 queries, q head, batch element[, share of the keys]), longest
-// items first.  320 threads:
+// items first.  512 threads in four warpgroups, registers re-dealt between them with setmaxnreg (80 / 184 / 184 / 64):
 //   warp 0      TMA producer: the two Q tiles of an item, then its K and V tiles of 128 keys through two-deep rings
 //               that run on across items
 //   warp 1      MMA issuer, in this order per key tile j:  P0_j V_j, S0_{j+1}, P1_j V_j, S1_{j+1}; in the last step of
-//               an item the S_0 tiles of the NEXT item take the place of S_{j+1}
-//   warps 2-5   softmax of query tile 0          warps 6-9   softmax of query tile 1
+//               an item the S_0 tiles of the NEXT item take the place of S_{j+1}     (warps 2-3 idle)
+//   warps 4-7   softmax of query tile 0          warps 8-11  softmax of query tile 1
+//   warps 12-15 output: when an item's last P V of a query tile is done, O leaves tensor memory, is normalised, staged
+//               in shared memory and written with TMA stores -- while the softmax warpgroups are already on the next item
 // While one softmax warpgroup works on its S tile the tensor core serves the other tile, and each SM sub-partition
 // holds two softmax warps whose MUFU / FMA / TMEM latencies overlap.  K and V tiles are fetched once for 256 queries.
-// Across items the pipeline does not drain: while a warpgroup normalises and stores O of item i, the Q tiles of item
-// i+1 are already in shared memory and its first S tile is in tensor memory.
+// Across items the pipeline does not drain: the Q tiles of item i+1 are in shared memory and its first S tiles in
+// tensor memory before item i's output has left.
 //
 // Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
 // P_j (16-bit) is written back over the first 64 columns of its own S tile and is the A operand of P_j V_j straight
 // from tensor memory (no shared-memory round trip).  MMAs issued by one thread complete in issue order, so S_{j+1}
 // (issued after P_j V_j) cannot overwrite P_j early, and an arrival on s_full also means the previous P V is done.
-// The first P V of an item overwrites O, so it waits until the warpgroup has read the previous item's O (o_free).
+// The first P V of an item overwrites O, so it waits until the output warpgroup has read the previous item's O (o_free).
 //
 // One thread owns one query row.  (Two threads per row were measured slower on B200 -- 0.418 ms against 0.353 ms on
-// the Llama-3-8B B8 S2048 prefill: the row-max exchange and the register cap of a 576-thread CTA cost more than the
-// extra warps hide -- and so was a variant with P staged in shared memory.)
+// the Llama-3-8B B8 S2048 prefill: the row-max exchange costs more than the extra warps hide -- and so was a variant
+// with P staged in shared memory.)
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -34,7 +36,8 @@ namespace {
 
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int kThreads = 64 + 2 * 128;  // TMA warp, MMA warp, softmax warps of two query tiles
+constexpr int kThreads = 4 * 128;  // warpgroups: TMA + MMA (+2 idle warps), softmax of query tile 0, of tile 1, output
+constexpr int kRegsControl = 80, kRegsSoftmax = 184, kRegsOutput = 64;  // (80 + 184 + 184 + 64) * 128 = 65536
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;
@@ -44,8 +47,11 @@ template <int D> struct Smem2 {
   static constexpr int kQOff = 0;                 // two query tiles
   static constexpr int kKOff = 2 * kTile;         // two stages
   static constexpr int kVOff = 4 * kTile;         // two stages
-  static constexpr int kBarOff = 6 * kTile;
+  static constexpr int kOOff = 6 * kTile;         // one normalised output tile (16-bit) on its way to a TMA store
+  static constexpr int kStatOff = 7 * kTile;      // 2 x 128 floats: the factor each row of O is multiplied with
+  static constexpr int kBarOff = kStatOff + 1024;
   static constexpr int kTotal = kBarOff + 256 + 1024;
+  static_assert(kTotal <= 232448, "more shared memory than an sm_100 CTA can have");
 };
 
 // Division by a value fixed for the launch as a multiply and a shift: decoding an item takes four divisions, and as
@@ -67,7 +73,7 @@ __device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
 }
 
 struct Attn2Params {
-  CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_q, map_k, map_v, map_o;
   int B, S, Hq, Hkv, past, kv_len, causal;
   int n_blocks;      // blocks of 256 queries
   int n_items;       // n_blocks * kv_splits * Hq * B
@@ -136,8 +142,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   uint64_t* s_full = bars + 12;   // [2] per query tile
   uint64_t* p_ready = bars + 14;  // [2] per query tile
   uint64_t* pv_done = bars + 16;  // [2] per query tile
-  uint64_t* o_free = bars + 18;   // [2] per query tile: the warpgroup has read O of the item it finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* o_free = bars + 18;   // [2] per query tile: the output warpgroup has read O of the item that finished
+  uint64_t* stat_full = bars + 20;   // [2] per query tile: the softmax warpgroup has left the rows' output factors
+  uint64_t* stat_empty = bars + 22;  // [2] per query tile: the output warpgroup has read them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  float* stat = reinterpret_cast<float*>(smem + L::kStatOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -155,6 +164,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       mbar_init(&p_ready[i], 4);   // one arrival per warp of the warpgroup
       mbar_init(&pv_done[i], 1);
       mbar_init(&o_free[i], 4);
+      mbar_init(&stat_full[i], 4);
+      mbar_init(&stat_empty[i], 4);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -167,14 +178,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
     tma_prefetch_desc(&p.map_q);
     tma_prefetch_desc(&p.map_k);
     tma_prefetch_desc(&p.map_v);
+    tma_prefetch_desc(&p.map_o);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
+  const int wg = warp >> 2;
 
-  if (warp == 0) {
+  if (wg == 0) {
+   warpgroup_regs_release<kRegsControl>();
+   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     uint32_t ring = 0;               // K/V tiles loaded so far: stage = ring & 1, use = ring >> 1
     uint32_t q_loads[2] = {0, 0};    // Q tiles loaded so far, per query tile
@@ -221,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       }
       ring += static_cast<uint32_t>(it.nt_max);
     }
-  } else if (warp == 1) {
+   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc(IsBf16<T>::value, false, false, BQ, BKV);
     constexpr uint32_t idesc_o = make_idesc(IsBf16<T>::value, false, true, BQ, D);
@@ -331,15 +346,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       }
       cur = nxt;
     }
-  } else {
+   }
+  } else if (wg == 1 || wg == 2) {
     // ------------------------------------------------------------ softmax warps: a thread owns a query row
-    const int t = (warp - 2) >> 2;  // query tile
+    warpgroup_regs_take<kRegsSoftmax>();
+    const int t = wg - 1;           // query tile
     const int quad = warp & 3;      // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
     const int r_in = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + t * BKV + lane_sel;
     const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
-    uint32_t s_count = 0;  // S tiles consumed so far by this query tile, over all items
+    uint32_t s_count = 0;   // S tiles consumed so far by this query tile, over all items
+    uint32_t handed = 0;    // items whose output factors have been handed to the output warpgroup
     bool ok = true;
 
     for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
@@ -383,25 +401,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
           alpha = fast_exp2(m_use - m_new);
           m_use = m_new;
         }
-        const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
-        // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements
-        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-        const float2 nm2 = make_float2(neg_mref, neg_mref);
-        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-        uint32_t pk[BKV / 2];
-#pragma unroll
-        for (int c = 0; c < BKV; c += 4) {
-          const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, nm2);
-          const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sc2, nm2);
-          const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
-          const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
-          acc0 = __fadd2_rn(acc0, e0);
-          acc1 = __fadd2_rn(acc1, e1);
-          pk[c >> 1] = Pack2<T>::pack(e0.x, e0.y);
-          pk[(c >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
-        }
-        l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
-
         // s_full(j) arrived => P_{j-1} V_{j-1} of this tile has completed: O may be rescaled, P may be overwritten
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
           uint32_t o[32];
@@ -414,9 +413,29 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
             tmem_st_x32(tmem_o + c * 32, o);
           }
         }
+        const float neg_mref = (m_use == -INFINITY) ? 0.f : -m_use;
+        // packed fp32x2 arithmetic: one FMA and one ADD instruction per two elements; P leaves in two halves of 64 keys
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 nm2 = make_float2(neg_mref, neg_mref);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < BKV / 64; ++c)  // 64 keys = 32 packed columns per store
-          tmem_st_x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[c * 32]));
+        for (int h = 0; h < BKV / 64; ++h) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 64; c += 4) {
+            const int e = h * 64 + c;
+            const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sc2, nm2);
+            const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), sc2, nm2);
+            const float2 e0 = make_float2(fast_exp2(t0.x), fast_exp2(t0.y));
+            const float2 e1 = make_float2(fast_exp2(t1.x), fast_exp2(t1.y));
+            acc0 = __fadd2_rn(acc0, e0);
+            acc1 = __fadd2_rn(acc1, e1);
+            pk[c >> 1] = Pack2<T>::pack(e0.x, e0.y);
+            pk[(c >> 1) + 1] = Pack2<T>::pack(e1.x, e1.y);
+          }
+          tmem_st_x32(tmem_s + h * 32, pk);  // 64 keys = 32 packed columns
+        }
+        l = l * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -424,21 +443,72 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
       }
       if (!ok) break;
 
-      // ---- end of the item: O leaves tensor memory first (which lets the next item's P V start), then goes out
-      const bool have = my_nt > 0 && mbar_wait(&pv_done[t], (s_count - 1) & 1, ctx, 409);
-      if (my_nt > 0 && !have) { ok = false; break; }
+      // ---- end of the item: hand the factor each row of O is to be multiplied with to the output warpgroup (which
+      //      waits for the last P V itself) and go on to the next item at once
       const Item it = decode_item(p, i);
       const int qi = it.q0 + t * BQ + r_in;
       const bool row_ok = qi < p.S;
+      if (my_nt > 0) {
+        if (handed > 0 && !mbar_wait(&stat_empty[t], (handed - 1) & 1, ctx, 411)) { ok = false; break; }
+        stat[t * BQ + r_in] = (p.kv_splits > 1) ? 1.f : ((l > 0.f) ? 1.f / l : 0.f);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stat_full[t]);
+        ++handed;
+      }
       if (p.kv_splits > 1) {
-        // this item saw only a share of the keys: leave the unnormalised accumulator, its exponent reference and its
-        // row sum; attn_combine_kernel merges the shares.  A share without keys leaves the neutral element.
+        // this item saw only a share of the keys: its unnormalised accumulator, exponent reference and row sum are
+        // left for attn_combine_kernel.  A share without keys leaves the neutral element.
         const long long prow = ((static_cast<long long>(it.sp) * p.B + it.b) * p.Hq + it.hq) * p.S + qi;
-        if (have) tc_fence_after();
+        if (row_ok) {
+          p.part_ml[prow * 2] = my_nt > 0 ? m_use : -INFINITY;
+          p.part_ml[prow * 2 + 1] = my_nt > 0 ? l : 0.f;
+          if (my_nt == 0) {
+            uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D);
+#pragma unroll
+            for (int e = 0; e < D / 4; ++e) d[e] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      } else if (my_nt > 0 && row_ok && p.lse2 != nullptr) {
+        p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
+      }
+    }
+  } else if (wg == 3) {
+    // ------------------------------------------------------------ output warps: a thread owns a query row of O
+    warpgroup_regs_release<kRegsOutput>();
+    const int quad = warp & 3;
+    const int r_in = quad * 32 + lane;
+    const int tid = threadIdx.x - 3 * 128;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* stage = smem + L::kOOff;
+    uint32_t pv_total[2] = {0, 0};   // P V products of each query tile up to the end of the current item
+    uint32_t taken[2] = {0, 0};      // items whose factors have been taken, per query tile
+    bool store_pending = false;
+    bool ok = true;
+    for (int i = blockIdx.x; ok && i < p.n_items; i += gridDim.x) {
+      const Item it = decode_item(p, i);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int nt = t == 0 ? it.nt[0] : it.nt[1];
+        if (nt == 0) continue;
+        const uint32_t total = (t == 0 ? pv_total[0] : pv_total[1]) + static_cast<uint32_t>(nt);
+        const uint32_t seen = t == 0 ? taken[0] : taken[1];
+        if (t == 0) { pv_total[0] = total; ++taken[0]; } else { pv_total[1] = total; ++taken[1]; }
+        if (!mbar_wait(&stat_full[t], seen & 1, ctx, 412)) { ok = false; break; }
+        const float f = stat[t * BQ + r_in];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stat_empty[t]);
+        // The last P V of the item.  When the factors arrive, the P V before it is complete (the softmax warps saw the S
+        // tile that was issued behind it), so the barrier is at most one phase behind the one waited for.
+        if (!mbar_wait(&pv_done[t], (total - 1) & 1, ctx, 409)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_o = tmem_base + 2 * BKV + t * D + lane_sel;
+        const int q0t = it.q0 + t * BQ;
         uint32_t o[32];
+        if (p.kv_splits > 1) {
+          const int qi = q0t + r_in;
+          const long long prow = ((static_cast<long long>(it.sp) * p.B + it.b) * p.Hq + it.hq) * p.S + qi;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          if (have) {  // uniform over the warp
+          for (int c = 0; c < D / 32; ++c) {
             tmem_ld_x32(tmem_o + c * 32, o);
             tmem_wait_ld();
             if (c == D / 32 - 1) {
@@ -446,45 +516,49 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
               __syncwarp();
               if (lane == 0) mbar_arrive(&o_free[t]);
             }
-          } else {
+            if (qi < p.S) {
+              uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D + c * 32);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = 0u;
+              for (int e = 0; e < 8; ++e) d[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
+            }
           }
-          if (row_ok) {
-            uint4* d = reinterpret_cast<uint4*>(p.part_o + prow * D + c * 32);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) d[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
-          }
+          continue;
         }
-        if (row_ok) {
-          p.part_ml[prow * 2] = have ? m_use : -INFINITY;
-          p.part_ml[prow * 2 + 1] = have ? l : 0.f;
+        if (store_pending) {  // the previous tile's TMA stores have read the staging tile
+          if (tid == 0) tma_store_wait_read();
+          named_barrier_sync(1, 128);
         }
-      } else if (have) {
-        tc_fence_after();
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-        uint32_t packed[D / 2];
-        uint32_t o[32];
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           tmem_ld_x32(tmem_o + c * 32, o);
           tmem_wait_ld();
+          if (c == D / 32 - 1) {  // O has left tensor memory: the next item's first P V may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[t]);
+          }
+          // row r_in of the 64-column box c / 2, 128-byte swizzle: 16-byte chunk k of a row sits at k ^ (row & 7)
+          uint8_t* row = stage + (c >> 1) * (BQ * 128) + r_in * 128;
 #pragma unroll
-          for (int e = 0; e < 16; ++e)
-            packed[c * 16 + e] = Pack2<T>::pack(__uint_as_float(o[2 * e]) * inv_l, __uint_as_float(o[2 * e + 1]) * inv_l);
+          for (int k = 0; k < 4; ++k) {
+            const uint4 v = make_uint4(Pack2<T>::pack(__uint_as_float(o[8 * k]) * f, __uint_as_float(o[8 * k + 1]) * f),
+                                       Pack2<T>::pack(__uint_as_float(o[8 * k + 2]) * f, __uint_as_float(o[8 * k + 3]) * f),
+                                       Pack2<T>::pack(__uint_as_float(o[8 * k + 4]) * f, __uint_as_float(o[8 * k + 5]) * f),
+                                       Pack2<T>::pack(__uint_as_float(o[8 * k + 6]) * f, __uint_as_float(o[8 * k + 7]) * f));
+            *reinterpret_cast<uint4*>(row + ((((c & 1) * 4 + k) ^ (r_in & 7)) << 4)) = v;
+          }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[t]);
-        if (row_ok) {
-          T* orow = static_cast<T*>(p.o2) + ((static_cast<long long>(it.b) * p.S + qi) * p.Hq + it.hq) * D;
-          uint4* d = reinterpret_cast<uint4*>(orow);
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (tid == 0) {  // rows beyond S are clipped by the tensor map
 #pragma unroll
-          for (int e = 0; e < D / 8; ++e) d[e] = make_uint4(packed[4 * e], packed[4 * e + 1], packed[4 * e + 2], packed[4 * e + 3]);
+          for (int dc = 0; dc < D / 64; ++dc) tma_store_3d(&p.map_o, stage + dc * (BQ * 128), it.hq * D + dc * 64, q0t, it.b);
+          tma_store_commit();
         }
-        if (row_ok && p.lse2 != nullptr) p.lse2[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.S + qi] = m_use + log2f(l);
+        store_pending = true;
       }
     }
+    if (tid == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -594,6 +668,12 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream) {
     const uint32_t box[3] = {64, BKV, 1};
     if ((status = make_tensor_map(&p.map_k, a.k_cache, 3, dims, strides, box)) != TB200_OK) return status;
     if ((status = make_tensor_map(&p.map_v, a.v_cache, 3, dims, strides, box)) != TB200_OK) return status;
+  }
+  {  // o2 (B, S, Hq*D): a box is 128 query rows of one head's 64 columns; rows past S are clipped per batch element
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.Hq) * D, static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.B)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(a.Hq) * D * 2, static_cast<uint64_t>(a.S) * a.Hq * D * 2};
+    const uint32_t box[3] = {64, BQ, 1};
+    if ((status = make_tensor_map(&p.map_o, a.o2, 3, dims, strides, box)) != TB200_OK) return status;
   }
   p.n_blocks = (a.S + 2 * BQ - 1) / (2 * BQ);
   const long long items = static_cast<long long>(p.n_blocks) * p.kv_splits * a.Hq * a.B;

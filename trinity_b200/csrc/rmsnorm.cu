@@ -87,6 +87,44 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const T* __restrict__
   for (int v = threadIdx.x + kCachedVecs * kThreads; v < nvec; v += kThreads) scale_store(v, __ldg(xr + v));
 }
 
+// Row statistic only (inv_rms[r] = rsqrt(mean(x[r,:]^2) + eps)): the norm-as-epilogue path reads x once and writes four
+// bytes per row.  One WARP per row, warps walking the rows with a grid-wide stride; a lane keeps eight 16-byte loads in
+// flight, so a few resident warps per SM cover the HBM latency -- a CTA per row (the kernel above) spends most of an
+// 8 KiB row's time starting and ending CTAs.  The lane-order reduction is fixed: bit-identical run to run.
+template <typename T>
+__global__ void __launch_bounds__(256) row_stats_kernel(const T* __restrict__ x, float* __restrict__ inv_rms, int64_t rows, int cols,
+                                                         float eps, float divisor) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int nvec = cols >> 3;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+    float ss = 0.f;
+    for (int v0 = lane; v0 < nvec; v0 += 32 * 8) {
+      uint4 u[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + 32 * i;
+        u[i] = v < nvec ? __ldg(xr + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Pack2<T>::unpack(w[j]);
+          ss = fmaf(f.x, f.x, ss);
+          ss = fmaf(f.y, f.y, ss);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) inv_rms[row] = rsqrtf(ss / divisor + eps);
+  }
+}
+
 // out[k, :] = w[k, :] * g[k]: the norm weight folded into the rows of a (K, N) projection weight, so that
 // (x * r * g) @ W = r * (x @ (diag(g) W)) and the weighted norm costs the projection nothing but its row scale.
 template <typename T>
@@ -137,6 +175,22 @@ int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, i
   if (rows == 0) return TB200_OK;
   const dim3 grid(static_cast<unsigned>(rows));
   const float divisor = static_cast<float>(mean_divisor > 0 ? mean_divisor : cols);
+  if (y == nullptr && rows >= 64) {  // statistic only, enough rows to fill the machine with warps
+    int status = TB200_OK;
+    DeviceState* st = device_state(&status);
+    if (!st) return status;
+    int64_t blocks = (rows + 7) / 8;
+    if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
+    if (dtype == TB200_BF16)
+      row_stats_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), inv_rms, rows,
+                                                                                       static_cast<int>(cols), eps, divisor);
+    else if (dtype == TB200_F16)
+      row_stats_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __half*>(x), inv_rms, rows, static_cast<int>(cols),
+                                                                                eps, divisor);
+    else
+      return TB200_ERR_UNSUPPORTED;
+    return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  }
   if (dtype == TB200_BF16) {
     rmsnorm_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
                                                               static_cast<const __nv_bfloat16*>(weight),
