@@ -113,6 +113,44 @@ int tb200_gemm_check(const tb200_gemm_args* args);
 int tb200_gemm_static_scratch(const tb200_gemm_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel row-parallel projection with its all-reduce done by the kernels over peer memory (NVLink):
+ * out = sum over ranks of (a_r @ b_r) [+ residual], every rank ending with the full (m, n) result.  No counterpart in
+ * the reference, which has no multi-GPU path; it stands where "tb200_gemm, then ncclAllReduce" would, for the down
+ * projection of a tensor-parallel FFN (a: this rank's columns of the activated inner tensor, (m, k_local); b: this
+ * rank's rows of W_down, (k_local, n)).  One process per GPU; `world` <= 8 ranks on one NVSwitch domain.
+ *   - Rank r owns rows [r*m/world, (r+1)*m/world) of the result; m % (128*world) == 0.
+ *   - stage[q], out[q], sync[q] are rank q's buffers as seen from THIS process: this rank's own allocations for
+ *     q == rank, peer mappings (tb200_ipc_open of what rank q exported) otherwise.  stage: tb200_peer_stage_bytes;
+ *     out: m*n 16-bit values; sync: tb200_peer_sync_bytes, zeroed once when the communicator is set up.
+ *   - epoch: 1 for the first call on these buffers, then 2, 3, ... -- the same on all ranks; the buffers serve ONE
+ *     shape (m, n, world).  All ranks must make the call (it ends with a rank-to-rank completion exchange); `out` of a
+ *     call must have been consumed, on this stream, before the next call.
+ *   - Every device-side wait on a peer is bounded (tb200_set_wait_limit_cycles); a rank that never arrives shows up as
+ *     TB200_ERR_DEVICE_TIMEOUT in tb200_device_status, code 601 (contributions) or 602 (completion).
+ *   - The sum is taken in rank order in fp32 from the ranks' 16-bit partial products: the same bits on every run and
+ *     on every rank. */
+typedef struct {
+  int dtype;                 /* TB200_F16 or TB200_BF16 */
+  int world, rank;
+  int64_t m, n, k;           /* k = this rank's share of the contraction */
+  const void* a;             /* (m, k) */
+  const void* b;             /* (k, n) */
+  const void* residual;      /* (m, n) or NULL: added once, by the row's owner (identical on all ranks) */
+  void* stage[8];
+  void* out[8];
+  void* sync[8];
+  uint32_t epoch;
+} tb200_peer_gemm_args;
+size_t tb200_peer_stage_bytes(int64_t m, int64_t n);
+size_t tb200_peer_sync_bytes(int64_t m, int world);
+int tb200_gemm_peer_reduce(const tb200_peer_gemm_args* args, void* stream);
+/* CUDA IPC plumbing for the buffers above (one process per GPU): export a device pointer as a 64-byte handle plus its
+ * offset inside the underlying allocation; open what another process exported; close it again. */
+int tb200_ipc_export(const void* ptr, void* handle64, int64_t* offset_out);
+int tb200_ipc_open(const void* handle64, int64_t offset, void** ptr_out);
+int tb200_ipc_close(void* ptr, int64_t offset);
+
+/* ---------------------------------------------------------------------------------------------
  * Fused attention block -- replaces kernel_0/kernel_1 of the emitted attention modules:
  *   Vanilla   evaluation/vanilla/vanilla_falcon_benchmark28173.py:19-144  (baseline/ref_rms.py:44-82)
  *   PreNorm   evaluation/prenorm/prenorm_falcon_benchmark579.py:19-120    (ref_rms.py:100-126)

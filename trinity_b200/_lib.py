@@ -52,6 +52,16 @@ class FfnArgs(C.Structure):
     ]
 
 
+class PeerGemmArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("residual", C.c_void_p),
+        ("stage", C.c_void_p * 8), ("out", C.c_void_p * 8), ("sync", C.c_void_p * 8),
+        ("epoch", C.c_uint32),
+    ]
+
+
 class KvCompactArgs(C.Structure):
     _fields_ = [
         ("dtype", C.c_int), ("rows", C.c_int), ("head_dim", C.c_int), ("kv_len", C.c_int),
@@ -77,6 +87,12 @@ SYMBOLS = {
     "tb200_gemm_workspace_bytes": (C.c_size_t, [C.POINTER(GemmArgs)]),
     "tb200_gemm": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "tb200_gemm_static_scratch": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "tb200_peer_stage_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "tb200_peer_sync_bytes": (C.c_size_t, [C.c_int64, C.c_int]),
+    "tb200_gemm_peer_reduce": (C.c_int, [C.POINTER(PeerGemmArgs), C.c_void_p]),
+    "tb200_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),
+    "tb200_ipc_open": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p)]),
+    "tb200_ipc_close": (C.c_int, [C.c_void_p, C.c_int64]),
     "tb200_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "tb200_attn_forward": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "tb200_attn_forward_timed": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.POINTER(C.c_float)]),

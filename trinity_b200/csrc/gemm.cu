@@ -39,6 +39,11 @@ constexpr int kBBytes = 4 * kBChunkBytes;    // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + slack to align the ring to 1 KiB
+// GEMM_PEER: two staged boxes of 128 rows x 64 columns, 1 KiB-aligned (their swizzle is a function of the address),
+// behind the barrier block padded to 1 KiB
+constexpr int kPeerStageOff = kStages * kStageBytes + 1024;
+constexpr int kPeerSmemBytes = kPeerStageOff + 2 * BM * 128 + 1024;
+static_assert(kPeerSmemBytes <= 232448, "more shared memory than an sm_100 CTA can have");
 constexpr int kThreads = 192;
 constexpr int kGroupRows = 4096;  // rows of A whose tiles are walked across all column tiles before moving down
 constexpr int kTmemCols = 512;
@@ -79,6 +84,9 @@ struct GemmParams {
   const void* k_norm_weight;
   float* partial;
   long long ldp;
+  int world, rank, rows_per_rank;
+  CUtensorMap map_peer[kMaxPeers];   // GEMM_PEER: this rank's slot of every rank's staging buffer, (rows_per_rank, N)
+  unsigned* peer_counter[kMaxPeers];
 };
 
 struct Unit {
@@ -274,6 +282,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    unsigned* peer_pending = nullptr;  // GEMM_PEER: the counter the last tile has yet to arrive on
+    uint32_t peer_boxes = 0;           // GEMM_PEER: boxes staged so far
     for (int u = unit0; u < p.total_units; u += unit_step) {
       const Unit t = decode_unit<PAIR>(p, u, rank);
       if (!wait_bar<PAIR>(&tfull[acc], acc_phase, ctx, 104)) break;
@@ -337,6 +347,56 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             store32_clipped<T>(static_cast<T*>(p.C) + row * p.ldc + col, v, min(32, n_total - col));
           }
         }
+      } else if (MODE == GEMM_PEER) {
+        // The CTA's 128 rows of this tile lie in one 128-row block of one owner.  The four epilogue warps stage the
+        // tile as 16-bit values, 64 columns at a time, in two alternating shared-memory boxes, and one thread sends
+        // each box into the owner's staging buffer (its own memory or a peer's over NVLink) with a TMA store -- whole
+        // 128-byte lines on the wire.  The arrival on the owner's counter for a tile is sent when the NEXT tile's
+        // epilogue starts (or after the loop): by then its stores have long completed, nobody waits for the link.
+        const int n_total = p.src_n[0];
+        const int owner = t.m0 / p.rows_per_rank;
+        const int local0 = t.m0 - owner * p.rows_per_rank;
+        const bool leader = warp == 2 && lane == 0;
+        uint8_t* stage = smem + kPeerStageOff;   // two boxes of 128 rows x 64 columns x 2 bytes
+        if (leader && peer_pending != nullptr) {
+          tma_store_wait_all();
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_pending) : "memory");
+          peer_pending = nullptr;
+        }
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          const int col = t.n0 + cb * 64;
+          if (col >= n_total) break;  // uniform over the four warps
+          uint8_t* box = stage + (peer_boxes & 1) * (BM * 128);
+          if (peer_boxes >= 2) {  // the store that last used this box has read it
+            if (leader) tma_store_wait_read_but_one();
+            named_barrier_sync(1, 128);
+          }
+          ++peer_boxes;
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            tmem_ld_x32(taddr + cb * 64 + cc * 32, r);
+            tmem_wait_ld();
+            // row (quad * 32 + lane) of the box, 128-byte swizzle: 16-byte chunk k of a row sits at k ^ (row & 7)
+            const int rr = quad * 32 + lane;
+            uint8_t* rowp = box + rr * 128;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint4 v4 = make_uint4(Pack2<T>::pack(__uint_as_float(r[8 * k]), __uint_as_float(r[8 * k + 1])),
+                                          Pack2<T>::pack(__uint_as_float(r[8 * k + 2]), __uint_as_float(r[8 * k + 3])),
+                                          Pack2<T>::pack(__uint_as_float(r[8 * k + 4]), __uint_as_float(r[8 * k + 5])),
+                                          Pack2<T>::pack(__uint_as_float(r[8 * k + 6]), __uint_as_float(r[8 * k + 7])));
+              *reinterpret_cast<uint4*>(rowp + (((cc * 4 + k) ^ (rr & 7)) << 4)) = v4;
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (leader) {  // columns past n_total are clipped by the tensor map
+            tma_store_2d(&p.map_peer[owner], box, col, local0);
+            tma_store_commit();
+          }
+        }
+        if (leader) peer_pending = p.peer_counter[owner] + (local0 >> 7);
       } else if (MODE == GEMM_PARTIAL) {
         int n_total = 0, col_base = 0;
         for (int s = 0; s < p.n_src; ++s) {
@@ -423,6 +483,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if (MODE == GEMM_PEER && warp == 2 && lane == 0) {
+      tma_store_wait_all();
+      if (peer_pending != nullptr) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_pending) : "memory");
     }
   }
 
@@ -542,8 +606,9 @@ int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cudaLaunchAttribute attr[1];
+  constexpr int kSmem = MODE == GEMM_PEER ? kPeerSmemBytes : kSmemBytes;
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
   if (PAIR) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -554,7 +619,7 @@ int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
     cfg.numAttrs = 1;
   }
   if (!attr_set[dev & 31]) {
-    if (cudaFuncSetAttribute(gemm_kernel<T, MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_kernel<T, MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return TB200_ERR_CUDA;
     if (PAIR) {
       cfg.gridDim = dim3(static_cast<unsigned>(slots / 2 * 2), 1, 1);
@@ -580,6 +645,7 @@ int launch_typed(const GemmParams& p, int mode, int slots, cudaStream_t stream) 
     case GEMM_SWIGLU: return launch_mode<T, GEMM_SWIGLU, PAIR>(p, slots, stream);
     case GEMM_QKV: return launch_mode<T, GEMM_QKV, PAIR>(p, slots, stream);
     case GEMM_PARTIAL: return launch_mode<T, GEMM_PARTIAL, PAIR>(p, slots, stream);
+    case GEMM_PEER: return launch_mode<T, GEMM_PEER, PAIR>(p, slots, stream);
     default: return TB200_ERR_UNSUPPORTED;
   }
 }
@@ -636,6 +702,13 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     if (g.C == nullptr || !aligned16(g.C) || (g.ldc & 7) != 0 || !aligned16(g.residual) || (g.ldr & 7) != 0) return TB200_ERR_INVALID;
   }
   if (g.mode == GEMM_PARTIAL && (g.partial == nullptr || !aligned16(g.partial))) return TB200_ERR_INVALID;
+  if (g.mode == GEMM_PEER) {
+    if (g.n_src != 1 || g.world < 1 || g.world > kMaxPeers || g.rank < 0 || g.rank >= g.world) return TB200_ERR_INVALID;
+    if (g.rows_per_rank <= 0 || (g.rows_per_rank & 127) != 0 || static_cast<long long>(g.rows_per_rank) * g.world != g.M) return TB200_ERR_INVALID;
+    for (int r = 0; r < g.world; ++r)
+      if (g.peer_stage[r] == nullptr || !aligned16(g.peer_stage[r]) || g.peer_counter[r] == nullptr || !aligned4(g.peer_counter[r]))
+        return TB200_ERR_INVALID;
+  }
   if (g.mode == GEMM_QKV && g.N[1] <= BN / 2 && g.N[2] <= BN / 2) {  // MQA / small GQA: K and V share one tile
     p.kv_merged = 1;
     tiles = p.src_tile0[1] + 1;
@@ -672,6 +745,17 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.q_norm_weight = g.q_norm_weight;
   p.k_norm_weight = g.k_norm_weight;
   p.partial = g.partial;
+  p.world = g.world; p.rank = g.rank; p.rows_per_rank = g.rows_per_rank;
+  for (int r = 0; r < kMaxPeers; ++r) p.peer_counter[r] = g.peer_counter[r];
+  if (g.mode == GEMM_PEER) {
+    for (int r = 0; r < g.world; ++r) {  // this rank's slot of rank r's staging buffer: (rows_per_rank, N) 16-bit values
+      const uint64_t dims[2] = {static_cast<uint64_t>(g.N[0]), static_cast<uint64_t>(g.rows_per_rank)};
+      const uint64_t strides[1] = {static_cast<uint64_t>(g.N[0]) * 2};
+      const uint32_t box[2] = {64, BM};
+      const uint8_t* slot = static_cast<const uint8_t*>(g.peer_stage[r]) + static_cast<size_t>(g.rank) * g.rows_per_rank * g.N[0] * 2;
+      if ((status = make_tensor_map(&p.map_peer[r], slot, 2, dims, strides, box)) != TB200_OK) return status;
+    }
+  }
   long long ldp = 0;
   for (int s = 0; s < g.n_src; ++s) ldp += g.N[s];
   p.ldp = ldp;

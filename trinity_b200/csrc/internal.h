@@ -48,8 +48,12 @@ enum GemmMode {
   GEMM_STORE = 0,    // c = act(acc * row_scale) + residual
   GEMM_SWIGLU = 1,   // two B sources of equal width: c = silu(acc0 * rs) * (acc1 * rs)
   GEMM_QKV = 2,      // three B sources (Wq, Wk, Wv): head split, optional per-head RMSNorm, cache append
-  GEMM_PARTIAL = 3   // fp32 partial sums of one K slice into the workspace
+  GEMM_PARTIAL = 3,  // fp32 partial sums of one K slice into the workspace
+  GEMM_PEER = 4      // tensor-parallel partial product: every 128-row block of the result goes, as 16-bit values, into the
+                     // staging buffer of the rank that owns those rows (a peer pointer), followed by an arrival on that
+                     // rank's counter for the block; peer.cu sums the ranks' contributions
 };
+constexpr int kMaxPeers = 8;
 struct GemmLaunch {
   int dtype = TB200_BF16;
   int mode = GEMM_STORE;
@@ -78,6 +82,11 @@ struct GemmLaunch {
   // GEMM_PARTIAL
   int split_k = 1;
   float* partial = nullptr;         // (split_k, M, sum N[i])
+  // GEMM_PEER: rows [r * rows_per_rank, (r + 1) * rows_per_rank) belong to rank r; rank r's staging buffer holds
+  // (world, rows_per_rank, N[0]) 16-bit values, slot `rank` is this rank's; counters are one uint32 per 128 owned rows
+  int world = 1, rank = 0, rows_per_rank = 0;
+  void* peer_stage[kMaxPeers] = {};
+  unsigned* peer_counter[kMaxPeers] = {};
 };
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 

@@ -117,13 +117,19 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
                         norm: bool = False, norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
                         falcon_tail: bool = False, group=None, local_ops=None,
                         all_reduce: Optional[Callable[[torch.Tensor], None]] = None,
-                        overlap_chunks: Optional[int] = None) -> Dict[str, torch.Tensor]:
+                        overlap_chunks: Optional[int] = None, peer=None) -> Dict[str, torch.Tensor]:
     """One FFN block, tensor-parallel over the ranks of ``group``.
 
     ``x`` (T,N) is replicated; ``o2_local`` (T,N/g) is this rank's column shard of the attention output when the block
     starts with ``O2 @ WO + X``.  Returns ``{"FF2": ..}`` (replicated after the all-reduce) or, with ``falcon_tail``,
     ``{"O_FF": FF2 + h, "O_FF_norm": RMSNorm(O_FF)}``.  Residuals are added on rank 0 only, before the all-reduce, so
     that the sum carries them exactly once.
+
+    With ``peer`` (a ``trinity_b200.peer.PeerReduce`` set up for ``(T, N)``) the down projection and its all-reduce are
+    ONE pair of kernels that exchange over peer memory: the projection's epilogue stores every 128-row block of its partial
+    product into the block owner's staging buffer while its main loop runs on, and a second kernel sums the ranks'
+    contributions in rank order and writes the result into every rank's buffer (``tb200_gemm_peer_reduce``).  No NCCL
+    call is made for that step; the result is the communicator's buffer, overwritten by the next call.
 
     With ``overlap_chunks`` > 1 the down projection and its all-reduce are pipelined over that many blocks of token
     rows: the sum of block i travels (asynchronous collective, the library's own stream) while block i+1 is multiplied.
@@ -162,7 +168,9 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
         ff1 = lo.gemm(h, shard.w_gate, row_scale=row_scale, act=1)
     else:
         ff1 = lo.gemm(h, shard.w_gate, b2=shard.w_up, row_scale=row_scale)
-    if overlap_chunks > 1 and world > 1:
+    if peer is not None and world > 1:
+        ff2 = peer.gemm_reduce(ff1, shard.w_down, residual=h if falcon_tail else None)
+    elif overlap_chunks > 1 and world > 1:
         T = ff1.shape[0]
         step = -(-T // overlap_chunks)
         if T >= 128 * overlap_chunks:
