@@ -191,25 +191,35 @@ class ClockSampler:
 
 
 def bind_to_gpu_numa_node(local: int):
-    """Run this process (and so first-touch its pinned host buffers) on the CPUs of the NUMA node the GPU hangs off.
-    With all ranks on one node, eight ranks' host copies share one socket's memory controllers.  Returns the node or None."""
+    """Run this process (and so first-touch its pinned host buffers) on the CPUs next to its GPU.  With all ranks on one
+    NUMA node, eight ranks' host copies share one socket's memory controllers and cross the socket link.  The CPU set is
+    NVML's "ideal CPU affinity" of the device, else the cpulist of the PCI device's NUMA node.  Returns what was done."""
     try:
-        bus = torch.cuda.get_device_properties(local).pci_bus_id
-        dom = getattr(torch.cuda.get_device_properties(local), "pci_domain_id", 0)
-        dev = getattr(torch.cuda.get_device_properties(local), "pci_device_id", 0)
-        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (dom, bus, dev)
-        node = int(open(path).read().strip())
-        if node < 0:
-            return None
-        cpus = set()
-        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
-            a, _, b = part.partition("-")
-            cpus.update(range(int(a), int(b or a) + 1))
-        allowed = cpus & os.sched_getaffinity(0)
-        if not allowed:
-            return None
-        os.sched_setaffinity(0, allowed)
-        return node
+        allowed = os.sched_getaffinity(0)
+        cpus, how = set(), None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip().isdigit()]
+            h = nv.nvmlDeviceGetHandleByIndex(int(vis[local]) if local < len(vis) else local)
+            words = (max(allowed) // 64) + 1
+            mask = nv.nvmlDeviceGetCpuAffinity(h, words)
+            cpus = {64 * i + b for i, wd in enumerate(mask) for b in range(64) if (wd >> b) & 1}
+            how = "nvml cpu affinity"
+        except Exception:
+            pr = torch.cuda.get_device_properties(local)
+            path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (getattr(pr, "pci_domain_id", 0), pr.pci_bus_id, getattr(pr, "pci_device_id", 0))
+            node = int(open(path).read().strip())
+            if node >= 0:
+                for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                    a_, _, b_ = part.partition("-")
+                    cpus.update(range(int(a_), int(b_ or a_) + 1))
+                how = f"numa node {node}"
+        use = cpus & allowed
+        if not use or use == allowed:
+            return None if not use else f"{how}: already there ({len(use)} cpus)"
+        os.sched_setaffinity(0, use)
+        return f"{how}: {len(use)} of {len(allowed)} cpus"
     except Exception:
         return None
 
@@ -519,7 +529,15 @@ def partition_legs(args, d: Dist):
             it[0] += 1
             return shard.tensor_parallel_ffn(x, sets[it[0] & 1], act="swiglu")["FF2"]
 
-        m = measure(step, max(4, args.steps // 2), 3, d, min_region_s=0.4, burst_passes=10)
+        from trinity_b200.peer import PeerReduce
+        comm = PeerReduce(M, N, dtype, d.dev)
+
+        def fused_step():
+            it[0] += 1
+            return shard.tensor_parallel_ffn(x, sets[it[0] & 1], act="swiglu", peer=comm)["FF2"]
+
+        m = measure(fused_step, max(4, args.steps // 2), 3, d, min_region_s=0.4, burst_passes=10)
+        m_nccl = measure(step, max(4, args.steps // 2), 3, d, min_region_s=0.4, burst_passes=10)
         buf = step()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for _ in range(3):
@@ -531,13 +549,19 @@ def partition_legs(args, d: Dist):
         e1.record()
         d.barrier()
         ar_ms, = d.max(e0.elapsed_time(e1) / 20)
+        comm.close()
         flops = 2.0 * M * N * P * 3
         out["tensor_parallel_ffn"] = {
-            "workload": TP_FFN_LEG, "scaling": "strong", "collective": "one NCCL all-reduce (sum) of (tokens, hidden) bf16",
+            "workload": TP_FFN_LEG, "scaling": "strong",
+            "collective": "the down projection's epilogue sends its tiles to their owner rank over NVLink (TMA stores to peer memory), a second "
+                          "kernel sums in rank order and writes every rank's result (tb200_gemm_peer_reduce); no NCCL call in the block",
             "ms_per_pass": m["ms_per_pass"], "value": flops / (m["ms_per_pass"] * 1e-3) / 1e12, "unit": "TFLOP/s (whole job)",
-            "timed_region_s": m["region_s"], "burst_ms_per_pass": m["burst_ms_per_pass"], "allreduce_ms": ar_ms,
-            "allreduce_bytes": M * N * 2, "allreduce_busbw_gbs": M * N * 2 * 2 * (d.world - 1) / d.world / (ar_ms * 1e-3) / 1e9,
-            "allreduce_share_of_pass": ar_ms / m["ms_per_pass"]}
+            "timed_region_s": m["region_s"], "burst_ms_per_pass": m["burst_ms_per_pass"],
+            "with_nccl_allreduce": {"ms_per_pass": m_nccl["ms_per_pass"], "value": flops / (m_nccl["ms_per_pass"] * 1e-3) / 1e12,
+                                    "burst_ms_per_pass": m_nccl["burst_ms_per_pass"], "allreduce_ms": ar_ms, "allreduce_bytes": M * N * 2,
+                                    "allreduce_busbw_gbs": M * N * 2 * 2 * (d.world - 1) / d.world / (ar_ms * 1e-3) / 1e9,
+                                    "allreduce_share_of_pass": ar_ms / m_nccl["ms_per_pass"],
+                                    "note": "the same block with GEMM, then one NCCL all-reduce (sum) of (tokens, hidden) bf16"}}
     return out
 
 
@@ -586,7 +610,7 @@ def run_attention(args, w, name):
                        "h2d_bytes_per_step": h2d * m["passes_per_step"], "d2h_bytes_per_step": d2h * m["passes_per_step"],
                        "h2d_bytes_per_pass": h2d, "d2h_bytes_per_pass": d2h,
                        "h2d_gbs_per_rank": h2d / (ms_e2e * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (ms_e2e * 1e-3) / 1e9,
-                       "host_numa_node_rank0": d.numa_node,
+                       "host_cpu_binding_rank0": d.numa_node,
                        "api": "generated-module forward(*TENSOR_PARAMS" + (", **" + "/".join(sorted(blk.extra)) + ")" if blk.extra else ")"),
                        "overlap": "upload / kernels / download on three streams, two buffers",
                        "resident": "noise tensor generated and kept on the device" if flags & L.ATTN_KEYFORMER else None}
@@ -683,12 +707,22 @@ def run_ffn(args, w, name):
     act = L.FFN_SWIGLU if gated else L.FFN_GELU
     it = [0]
 
+    comm = None
+    if world > 1 and M % (128 * world) == 0:
+        from trinity_b200.peer import PeerReduce
+        comm = PeerReduce(M, N, dtype, dev)
+
     def step():
         s_ = sets[it[0] % copies]
         it[0] += 1
         if world == 1:
             ops.ffn_forward(x, s_.w_gate, s_.w_up, s_.w_down, ff2, act=act)
             return ff2
+        return shard.tensor_parallel_ffn(x, s_, act=w["act"], peer=comm)["FF2"]
+
+    def nccl_step():
+        s_ = sets[it[0] % copies]
+        it[0] += 1
         return shard.tensor_parallel_ffn(x, s_, act=w["act"])["FF2"]
 
     sampler = ClockSampler(d.local)
@@ -725,6 +759,7 @@ def run_ffn(args, w, name):
         m["passes_per_step"] *= copies
     else:
         m = measure(step, args.steps, args.warmup, d)
+    m_nccl = measure(nccl_step, max(4, args.steps // 2), 3, d, min_region_s=0.4, burst_passes=10) if comm is not None else None
     ops.device_status()
     ms = m["ms_per_pass"]
     # stage split with the building-block GEMMs (same kernels the block chains)
@@ -787,7 +822,7 @@ def run_ffn(args, w, name):
                 ops.ffn_forward(x_dev[k], s_.w_gate, s_.w_up, s_.w_down, o_dev[k], act=act)
                 res = o_dev[k]
             else:
-                res = shard.tensor_parallel_ffn(x_dev[k], s_, act=w["act"])["FF2"]
+                res = shard.tensor_parallel_ffn(x_dev[k], s_, act=w["act"], peer=comm)["FF2"]
             ran[i].record(s_run)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ran[i])
@@ -831,7 +866,8 @@ def run_ffn(args, w, name):
             "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "us_per_call": ms * 1e3, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": workload_config(name, w),
-            "protocol": {"parallelism": "single GPU" if world == 1 else f"tensor-parallel x{world}, one NCCL all-reduce",
+            "protocol": {"parallelism": "single GPU" if world == 1 else (f"tensor-parallel x{world}, all-reduce inside the down projection's kernels over peer memory "
+                                                                         "(tb200_gemm_peer_reduce)" if comm is not None else f"tensor-parallel x{world}, one NCCL all-reduce"),
                          "l2": f"{copies} rotating weight sets of {weight_bytes / 1e6:.0f} MB each (> 126 MB L2)",
                          "timing": "CUDA-graph replay, as the reference harness" if use_graph else "stream launches"},
             "block_hbm_gbs": algo_bytes / world / (ms * 1e-3) / 1e9, "block_frac_of_hbm": algo_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
@@ -845,6 +881,9 @@ def run_ffn(args, w, name):
             "stages": {"up_ms": st_ms[0], "down_ms": st_ms[1]},
         }
         line.update(regime_fields(m, sampler, value_of))
+        if m_nccl is not None:
+            line["with_nccl_allreduce"] = {"ms_per_pass": m_nccl["ms_per_pass"], "value": value_of(m_nccl["ms_per_pass"]),
+                                           "note": "the same block with GEMM, then one NCCL all-reduce of (tokens, hidden)"}
         if not args.no_cpu_baseline:
             rows = min(M, 256)
             dt = time_cpu(lambda: orc.ffn_block(host["X"][:rows].float(), host["W_gate"].float(), host["W_up"].float() if gated else None,
@@ -852,6 +891,8 @@ def run_ffn(args, w, name):
             line["cpu_baseline"] = {"value": flops * rows / M / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "seconds": dt,
                                     "sample": f"{rows} of {M} tokens, 1 pass, fp32 oracle port of baseline/ffn_ref.py"}
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
     d.close()
 
 

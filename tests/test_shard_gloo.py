@@ -179,3 +179,38 @@ def test_slices_and_errors():
     assert [p.stop - p.start for p in parts] == [6, 5, 5] and parts[0].start == 0 and parts[-1].stop == 16
     with pytest.raises(ValueError):
         shard.shard_ffn_weights(torch.zeros(8, 20), torch.zeros(8, 20), torch.zeros(20, 8), None, 0, 2)
+
+
+def _absent_worker(rank, world, port, ret):
+    """Rank 1 joins the group and then never makes the collective (a stalled or dead peer); rank 0 must get an exception
+    from the host-side watchdog, not a hang.  The failure is made on the host: no GPU is involved."""
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        if rank == 1:
+            time.sleep(3.0)             # outlives rank 0's time limit, then leaves between steps
+            ret[rank] = "absent"
+            return
+        t0 = time.monotonic()
+        try:
+            shard.all_reduce_checked(torch.ones(4), timeout_s=1.0)
+            ret[rank] = "completed?!"
+        except shard.CollectiveTimeout as e:
+            ret[rank] = ("timeout", time.monotonic() - t0, str(e))
+    finally:
+        os._exit(0)                     # no orderly teardown with a peer that is not there
+
+
+def test_all_reduce_with_an_absent_rank_raises_instead_of_hanging():
+    port = _free_port()
+    ret = mp.Manager().dict()
+    procs = [mp.get_context("spawn").Process(target=_absent_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung"
+    assert ret[1] == "absent"
+    kind, waited, msg = ret[0]
+    assert kind == "timeout" and 0.9 < waited < 2.5 and "did not complete" in msg

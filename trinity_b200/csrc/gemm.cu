@@ -63,6 +63,7 @@ struct GemmParams {
   int tile_n;         // output columns per tile (256, or 128 for SwiGLU)
   int m_tiles, n_tiles, total_units;
   int group_m;        // row-tiles per L2 group
+  int mt_rotation;    // GEMM_PEER: row-tile this rank's walk starts at; 0 otherwise
   int kv_merged;      // GEMM_QKV with at most 128 columns each of Wk and Wv: one tile holds both (K in accumulator
                       // columns [0,128), V in [128,256)) instead of two tiles that are three quarters empty
   int* err;
@@ -113,7 +114,11 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u, int rank
   const int rem = tile - g * per_group;
   const int rows_here = min(kGroupM, p.m_tiles - g * kGroupM);
   const int nt = rem / rows_here;
-  const int mt = g * kGroupM + (rem - nt * rows_here);
+  int mt = g * kGroupM + (rem - nt * rows_here);
+  // GEMM_PEER: every rank starts its walk over the rows at its OWN rows and moves on from there, so that at any time
+  // the ranks send to different owners (a permutation over the links) instead of all to the same one
+  mt += p.mt_rotation;
+  if (mt >= p.m_tiles) mt -= p.m_tiles;
   r.m0 = PAIR ? (mt * 2 + rank) * BM : mt * BM;
   int src = 0;
   while (src + 1 < p.n_src && nt >= p.src_tile0[src + 1]) ++src;
@@ -748,6 +753,7 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.world = g.world; p.rank = g.rank; p.rows_per_rank = g.rows_per_rank;
   for (int r = 0; r < kMaxPeers; ++r) p.peer_counter[r] = g.peer_counter[r];
   if (g.mode == GEMM_PEER) {
+    p.mt_rotation = static_cast<int>(static_cast<long long>(g.rank) * p.m_tiles / g.world);
     for (int r = 0; r < g.world; ++r) {  // this rank's slot of rank r's staging buffer: (rows_per_rank, N) 16-bit values
       const uint64_t dims[2] = {static_cast<uint64_t>(g.N[0]), static_cast<uint64_t>(g.rows_per_rank)};
       const uint64_t strides[1] = {static_cast<uint64_t>(g.N[0]) * 2};

@@ -31,7 +31,7 @@ namespace {
 
 constexpr int kRbThreads = 256;
 constexpr int kRbRows = 128;      // rows per counter (one row block of the GEMM)
-constexpr int kRbCols = 512;      // columns per CTA
+constexpr int kRbCols = 256;      // columns per CTA
 
 struct ReduceParams {
   int world, rank, rows_per_rank, N;

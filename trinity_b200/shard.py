@@ -25,6 +25,36 @@ import torch
 import torch.distributed as dist
 
 
+class CollectiveTimeout(RuntimeError):
+    """A collective did not complete within the host-side time limit (a rank that never arrived, a failed link)."""
+
+
+def wait_collective(work, timeout_s: float, what: str = "collective") -> None:
+    """Poll an asynchronous collective until it completes, raises, or ``timeout_s`` passes.
+
+    ``torch.distributed`` surfaces NCCL's asynchronous errors on the work object (``exception()``); a rank that never
+    joins shows no error at all, only a collective that does not finish -- the host-side clock here is what turns that
+    into a ``CollectiveTimeout`` the caller can act on (drop the rank, rebuild the group) instead of a hang.  The wait
+    is on the host: nothing is enqueued behind the collective until it is known to have finished."""
+    import time
+    deadline = time.monotonic() + timeout_s
+    while True:
+        if work.is_completed():
+            exc = work.exception() if hasattr(work, "exception") else None
+            if exc is not None:
+                raise RuntimeError(f"{what} failed: {exc}")
+            return
+        if time.monotonic() > deadline:
+            raise CollectiveTimeout(f"{what} did not complete within {timeout_s:.1f} s")
+        time.sleep(0.0005)
+
+
+def all_reduce_checked(t: torch.Tensor, timeout_s: float, group=None) -> None:
+    """Sum-all-reduce ``t`` in place, or raise ``CollectiveTimeout`` / ``RuntimeError`` -- never hang."""
+    work = dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    wait_collective(work, timeout_s, "all-reduce")
+
+
 def _world(group=None) -> Tuple[int, int]:
     if dist.is_available() and dist.is_initialized():
         return dist.get_rank(group), dist.get_world_size(group)
@@ -117,7 +147,8 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
                         norm: bool = False, norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
                         falcon_tail: bool = False, group=None, local_ops=None,
                         all_reduce: Optional[Callable[[torch.Tensor], None]] = None,
-                        overlap_chunks: Optional[int] = None, peer=None) -> Dict[str, torch.Tensor]:
+                        overlap_chunks: Optional[int] = None, peer=None,
+                        collective_timeout_s: Optional[float] = None) -> Dict[str, torch.Tensor]:
     """One FFN block, tensor-parallel over the ranks of ``group``.
 
     ``x`` (T,N) is replicated; ``o2_local`` (T,N/g) is this rank's column shard of the attention output when the block
@@ -130,6 +161,9 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
     product into the block owner's staging buffer while its main loop runs on, and a second kernel sums the ranks'
     contributions in rank order and writes the result into every rank's buffer (``tb200_gemm_peer_reduce``).  No NCCL
     call is made for that step; the result is the communicator's buffer, overwritten by the next call.
+
+    ``collective_timeout_s`` puts a host-side clock on every NCCL all-reduce of the block (``all_reduce_checked``): a rank
+    that never arrives raises ``CollectiveTimeout`` on the others instead of hanging them.
 
     With ``overlap_chunks`` > 1 the down projection and its all-reduce are pipelined over that many blocks of token
     rows: the sum of block i travels (asynchronous collective, the library's own stream) while block i+1 is multiplied.
@@ -147,7 +181,10 @@ def tensor_parallel_ffn(x: torch.Tensor, shard: FfnShard, *, act: str = "swiglu"
     if all_reduce is None:
         def all_reduce(t):
             if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+                if collective_timeout_s is not None:     # host-side watchdog: a rank that never arrives raises instead of hanging
+                    all_reduce_checked(t, collective_timeout_s, group)
+                else:
+                    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     gelu = act == "gelu"
     if gelu == (shard.w_up is not None):
         raise ValueError("SwiGLU needs w_up; the GELU MLP takes none")
