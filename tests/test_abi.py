@@ -39,14 +39,15 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 def test_struct_layout_matches_header(tmp_path):
     from trinity_b200 import _lib
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "trinity_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "trinity_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+                   'sizeof(tb200_peer_gemm_args),offsetof(tb200_peer_gemm_args,epoch),'
                    'sizeof(tb200_gemm_args),sizeof(tb200_attn_args),sizeof(tb200_ffn_args),'
                    'offsetof(tb200_attn_args,workspace),offsetof(tb200_ffn_args,w_down),offsetof(tb200_gemm_args,split_k),'
                    'sizeof(tb200_kv_compact_args),offsetof(tb200_kv_compact_args,new_len));}')
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
     got = [int(v) for v in subprocess.check_output([str(exe)]).split()]
-    want = [C.sizeof(_lib.GemmArgs), C.sizeof(_lib.AttnArgs), C.sizeof(_lib.FfnArgs),
+    want = [C.sizeof(_lib.PeerGemmArgs), _lib.PeerGemmArgs.epoch.offset, C.sizeof(_lib.GemmArgs), C.sizeof(_lib.AttnArgs), C.sizeof(_lib.FfnArgs),
             _lib.AttnArgs.workspace.offset, _lib.FfnArgs.w_down.offset, _lib.GemmArgs.split_k.offset,
             C.sizeof(_lib.KvCompactArgs), _lib.KvCompactArgs.new_len.offset]
     assert got == want
