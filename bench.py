@@ -632,10 +632,24 @@ def run_attention(args, w, name):
             "burst": {"rmsnorm_ms": burst_stage[0], "qkv_gemm_ms": burst_stage[1], "attention_ms": burst_stage[2], "scores_ms": burst_stage[3],
                       "attention_tflops": attn_tf_burst, "attention_frac_of_peak": attn_tf_burst / peaks["bf16_tflops"] if attn_tf_burst else None}}
         if flags & L.ATTN_PRENORM and steady_stage[0] > 0:
-            # the norm weight is folded into the projection weights (ops.FoldedWeights): the stage is the row statistic, one read of x
-            norm_bytes = blk.B * blk.S * blk.N * 2 * (1 if ops.FoldedWeights.enabled or blk.kwargs["norm_weight"] is None else 2)
-            line["stages"]["rmsnorm_hbm_gbs"] = norm_bytes / (steady_stage[0] * 1e-3) / 1e9
+            # The norm weight is folded into the projection weights (ops.FoldedWeights): the stage is the row statistic, one
+            # read of x.  Inside the block it is the first launch after the host has waited for the previous call, so the
+            # event interval also holds the host's launch latency; the kernel is therefore timed back to back as well.
+            inv = torch.empty(blk.B * blk.S, dtype=torch.float32, device=d.dev)
+            for _ in range(3):
+                ops.row_inv_rms(blk.x, 1e-5, out=inv)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(50):
+                ops.row_inv_rms(blk.x, 1e-5, out=inv)
+            e1.record()
+            torch.cuda.synchronize()
+            alone_ms = e0.elapsed_time(e1) / 50
+            norm_bytes = blk.B * blk.S * blk.N * 2
+            line["stages"]["rmsnorm_kernel_alone_ms"] = alone_ms
+            line["stages"]["rmsnorm_hbm_gbs"] = norm_bytes / (alone_ms * 1e-3) / 1e9
             line["stages"]["rmsnorm_frac_of_hbm"] = line["stages"]["rmsnorm_hbm_gbs"] / peaks["hbm_gbs"]
+            line["stages"]["rmsnorm_note"] = "row statistic only (x read once, 268 MB > L2 at this size); the scale is applied in the projection's epilogue"
         if flags & (L.ATTN_ROCO | L.ATTN_KEYFORMER):
             line["stages"].update(score_stage_split(blk, steady_stage[3], peaks))
         line["block_frac_of_peak"] = total / d.world / (m["ms_per_pass"] * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"]
