@@ -37,7 +37,7 @@ def attention_case(B, S, N, Hq, Hkv, D, P, flags, dt=torch.bfloat16, scale=None,
     g = torch.Generator().manual_seed(seed)
     rn = lambda *s: torch.randn(*s, generator=g)
     x = rn(B, S, N)
-    wq, wk, wv = rn(N, Hq * D) * N ** -0.5, rn(N, Hkv * D) * N ** -0.5, rn(N, Hkv * D) * N ** -0.5
+    wq, wk, wv = rn(N, Hq * D) * 0.02, rn(N, Hkv * D) * 0.02, rn(N, Hkv * D) * 0.02     # the benchmark's distribution: N(0, 0.02)
     kc, vc = rn(B, Hkv, P + S + cache_extra, D), rn(B, Hkv, P + S + cache_extra, D)
     nw = (1 + 0.02 * rn(N)) if weights else None
     qw = (1 + 0.02 * rn(D)) if weights else None
