@@ -73,6 +73,33 @@ def test_gemm(ops, dt, M, N, K, opts):
     close(out, _gemm_ref(a, b, b2, rs, res, act), msg=f"gemm {M}x{N}x{K} {opts}")
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,opts", [
+    (64, 4096, 14336, {}), (16, 4544, 4544, dict(res=True)), (128, 4096, 4096, dict(rs=True, gelu=True)),
+    (100, 2048, 4104, dict(res=True, rs=True)), (64, 14336, 4096, dict(gated=True)), (16, 4544, 4544, dict(gated=True, rs=True)),
+    (1, 8192, 2048, {}), (64, 1032, 8192, {}),
+])
+def test_gemm_few_rows_wide_weights(ops, dt, M, N, K, opts):
+    """One row-tile of tokens against wide weights (the decode and 64-token shapes of the benchmark): with split_k = 0 the
+    library cuts K into slices until the SMs are filled and sums the slices in a fixed order.  Run twice: same bits."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(dt).to(dev())
+    b = (torch.randn(K, N, generator=g) * K ** -0.5).to(dt).to(dev())
+    b2 = (torch.randn(K, N, generator=g) * K ** -0.5).to(dt).to(dev()) if opts.get("gated") else None
+    rs = (torch.rand(M, generator=g) + 0.5).to(dev()) if opts.get("rs") else None
+    res = torch.randn(M, N, generator=g).to(dt).to(dev()) if opts.get("res") else None
+    act = 1 if opts.get("gelu") else 0
+    ref = _gemm_ref(a, b, b2, rs, res, act)
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=dt, device=dev())
+        ops.gemm(a, b, b2=b2, row_scale=rs, residual=res, act=act, split_k=0, out=out)
+        ops.device_status()
+        close(out, ref, msg=f"gemm {M}x{N}x{K} {opts}")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]), "two runs of the same problem differ"
+
+
 def test_gemm_is_deterministic(ops):
     g = torch.Generator().manual_seed(5)
     a = torch.randn(48, 4096, generator=g).to(torch.bfloat16).to(dev())
