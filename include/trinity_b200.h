@@ -53,6 +53,13 @@ int tb200_device_status(int* code_out);
  * after the call; process-wide.  No counterpart in the reference (Triton kernels have no such waits). */
 int tb200_set_wait_limit_cycles(long long cycles);
 long long tb200_get_wait_limit_cycles(void);
+/* Within one call (tb200_gemm, tb200_attn_forward, tb200_ffn_forward ...) the kernels after the first are launched
+ * with programmatic stream serialisation: each starts while the one before it drains, sets up, prefetches its
+ * weights, and waits (griddepcontrol.wait) before it touches anything a kernel of the call writes.  The first
+ * kernel of a call is an ordinary launch, so the call's arguments are complete before it starts.  Works inside
+ * stream capture.  0 switches this off (every launch ordinary), non-zero on (the default); returns the previous
+ * setting; process-wide.  The reference has no counterpart (its Triton kernels are launched one by one). */
+int tb200_set_chained_launch(int enabled);
 /* Test aid: launches a one-CTA kernel whose only mbarrier is never armed, with the given limit (1e3..2e9
  * cycles), through the same bounded-wait code as the compute kernels.  The wait runs out, the kernel
  * returns, and the next tb200_device_status reports TB200_ERR_DEVICE_TIMEOUT with code 900. */

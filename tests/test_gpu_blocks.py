@@ -38,13 +38,17 @@ def check_common(got, ref, P):
     (1, 200, 256, 2, 2, 128, 56, Pn, {}),                        # PreNorm reference point (no weight)
     (1, 130, 256, 2, 2, 128, 0, Q, {}),                          # QKNorm reference point
     (3, 129, 264, 3, 3, 64, 255, C | Q, dict(weights=True, cache_extra=40)),
-    # decode-sized query blocks (key range dealt out over several CTAs, shares merged by attn_combine_kernel)
+    # decode-sized query blocks: the one-kernel path (K-slice sums finished in the kernel when the projection is sliced,
+    # key shares merged inside a cluster)
     (2, 16, 512, 8, 2, 128, 1000, C, {}),                        # GQA, causal on a long cache, ragged last tile
     (1, 5, 256, 4, 4, 64, 63, C, dict(dt=torch.float16)),        # 5 tokens, the diagonal crosses a tile boundary
     (1, 16, 256, 4, 1, 64, 3, C | Pn | Q, dict(weights=True)),   # MQA, nearly empty cache, all norms
     (1, 1, 256, 2, 2, 128, 777, 0, dict(cache_extra=9)),         # one token, many shares
     (40, 3, 256, 16, 4, 128, 70, C, {}),                         # 640 heads in flight: one share per head, no merge
     (2, 9, 512, 4, 2, 128, 0, C, {}),                            # no cache at all
+    (2, 16, 512, 8, 2, 128, 1000, C | Pn | Q, dict(weights=True)),   # sliced projection: q, k finished and normalised in the attention kernel
+    (1, 13, 1024, 4, 4, 64, 300, Q, dict(weights=True, dt=torch.float16)),
+    (3, 16, 512, 4, 1, 128, 2049, 0, dict(cache_extra=5)),       # MQA: four q heads share the appended rows; 8 shares of 257 keys
 ])
 def test_attention_variants(B, S, N, Hq, Hkv, D, P, flags, kw):
     got, ref = attention_case(B, S, N, Hq, Hkv, D, P, flags, **kw)

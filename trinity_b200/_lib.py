@@ -78,6 +78,7 @@ SYMBOLS = {
     "tb200_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "tb200_set_wait_limit_cycles": (C.c_int, [C.c_longlong]),
     "tb200_get_wait_limit_cycles": (C.c_longlong, []),
+    "tb200_set_chained_launch": (C.c_int, [C.c_int]),
     "tb200_selftest_wait_timeout": (C.c_int, [C.c_longlong, C.c_void_p]),
     "tb200_gemm_check": (C.c_int, [C.POINTER(GemmArgs)]),
     "tb200_attn_check": (C.c_int, [C.POINTER(AttnArgs)]),

@@ -17,7 +17,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtrinity_b200.so")
-SOURCES = ["runtime.cu", "rmsnorm.cu", "gemm.cu", "attn.cu", "attn2.cu", "attn_kf.cu", "score.cu", "topk.cu", "evict.cu", "peer.cu", "api.cu"]
+SOURCES = ["runtime.cu", "rmsnorm.cu", "gemm.cu", "attn.cu", "attn2.cu", "attn_dec.cu", "attn_kf.cu", "score.cu", "topk.cu", "evict.cu", "peer.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -140,6 +140,7 @@ int tb200_gemm(const tb200_gemm_args* a, void* stream) {
   if (!st) return status;
   if ((status = check_gemm(a)) != TB200_OK) return status;
   if (a->m == 0) return TB200_OK;
+  ChainScope chain;
   GemmPlan pl = plan_gemm(a, st->num_sms);
   if (pl.split > 1 && (a->workspace == nullptr || a->workspace_bytes < pl.partial_bytes)) {
     if (a->split_k > 1) return TB200_ERR_WORKSPACE;  // the caller asked for slices but gave no room
@@ -247,6 +248,7 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
   if (a->workspace == nullptr || !aligned16(a->workspace)) return TB200_ERR_WORKSPACE;
   const AttnWs w = carve_attn(a, a->workspace, st->num_sms);
   if (a->workspace_bytes < w.bytes) return TB200_ERR_WORKSPACE;
+  ChainScope chain;
   const int T = a->batch * a->seq;
   const int D = a->head_dim;
 
@@ -267,6 +269,9 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
     if (status != TB200_OK) return status;
   }
   // 2. QKV projection with head split, optional per-head norm and cache append in the epilogue.
+  //    A block of at most 16 new tokens without a per-key statistic takes the one-kernel decode path after it.
+  const bool decode_path = !(a->flags & (TB200_ATTN_KEYFORMER | TB200_ATTN_ROCO)) && attn_decode_applies(a->batch, a->seq, a->n_q_heads, D);
+  AttnDecodeLaunch dec;
   if (ev) cudaEventRecord(ev[1], stream);
   {
     GemmLaunch g;
@@ -291,24 +296,42 @@ static int attn_forward_impl(const tb200_attn_args* a, void* stream_, cudaEvent_
       g.partial = w.partial;
       if ((status = launch_gemm(g, stream)) != TB200_OK) return status;
       const int k_blocks = (a->hidden + kBK - 1) / kBK, per = (k_blocks + w.split_qkv - 1) / w.split_qkv;
-      QkvFinish f;
-      f.dtype = a->dtype;
-      f.M = T;
-      f.split_k = (k_blocks + per - 1) / per;
-      f.partial = w.partial;
-      f.row_scale = row_scale;
-      f.q_out = w.q; f.k_cache = a->k_cache; f.v_cache = a->v_cache;
-      f.S = a->seq; f.Hq = a->n_q_heads; f.Hkv = a->n_kv_heads; f.D = D; f.past = a->past; f.cache_len = a->cache_len;
-      f.qknorm = g.qknorm; f.qk_eps = a->qk_eps;
-      f.q_norm_weight = a->q_norm_weight; f.k_norm_weight = a->k_norm_weight;
-      if ((status = launch_qkv_finish(f, stream)) != TB200_OK) return status;
-    } else if ((status = launch_gemm(g, stream)) != TB200_OK) {
-      return status;
+      if (decode_path) {  // the slices are summed, normalised and appended by the attention kernel itself
+        dec.partial = w.partial;
+        dec.split = (k_blocks + per - 1) / per;
+        dec.row_scale = row_scale;
+      } else {
+        QkvFinish f;
+        f.dtype = a->dtype;
+        f.M = T;
+        f.split_k = (k_blocks + per - 1) / per;
+        f.partial = w.partial;
+        f.row_scale = row_scale;
+        f.q_out = w.q; f.k_cache = a->k_cache; f.v_cache = a->v_cache;
+        f.S = a->seq; f.Hq = a->n_q_heads; f.Hkv = a->n_kv_heads; f.D = D; f.past = a->past; f.cache_len = a->cache_len;
+        f.qknorm = g.qknorm; f.qk_eps = a->qk_eps;
+        f.q_norm_weight = a->q_norm_weight; f.k_norm_weight = a->k_norm_weight;
+        if ((status = launch_qkv_finish(f, stream)) != TB200_OK) return status;
+      }
+    } else {
+      if ((status = launch_gemm(g, stream)) != TB200_OK) return status;
+      dec.q = w.q;
     }
+    dec.qknorm = g.qknorm;
+    dec.qk_eps = a->qk_eps;
+    dec.q_norm_weight = a->q_norm_weight;
+    dec.k_norm_weight = a->k_norm_weight;
   }
   // 3. softmax(QK^T)V
   if (ev) cudaEventRecord(ev[2], stream);
-  {
+  if (decode_path) {
+    dec.dtype = a->dtype;
+    dec.B = a->batch; dec.S = a->seq; dec.Hq = a->n_q_heads; dec.Hkv = a->n_kv_heads; dec.D = D; dec.past = a->past; dec.cache_len = a->cache_len;
+    dec.causal = (a->flags & TB200_ATTN_CAUSAL) ? 1 : 0;
+    dec.sm_scale = a->sm_scale;
+    dec.k_cache = a->k_cache; dec.v_cache = a->v_cache; dec.o2 = a->o2;
+    if ((status = launch_attn_decode(dec, stream)) != TB200_OK) return status;
+  } else {
     AttnLaunch f;
     f.dtype = a->dtype;
     f.B = a->batch; f.S = a->seq; f.Hq = a->n_q_heads; f.Hkv = a->n_kv_heads; f.D = D; f.past = a->past; f.cache_len = a->cache_len;
@@ -462,6 +485,7 @@ int tb200_ffn_forward(const tb200_ffn_args* a, void* stream_) {
   if (w.bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < w.bytes || !aligned16(a->workspace))) return TB200_ERR_WORKSPACE;
   const int M = static_cast<int>(a->tokens), N = static_cast<int>(a->hidden), P = static_cast<int>(a->inner);
   const bool norm = a->flags & TB200_FFN_NORM, tail = a->flags & TB200_FFN_FALCON_TAIL;
+  ChainScope chain;
 
   // a = o2 @ wo + x
   const void* act_in = a->x;

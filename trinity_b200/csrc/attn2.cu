@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd2_kernel(const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // q and the appended cache rows come from the kernel before this one
   const uint32_t tmem_base = *tmem_slot;
   const AbortCtx ctx{p.err, abort_flag, p.wait_limit};
   const int wg = warp >> 2;
@@ -574,6 +576,8 @@ template <typename T, int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ o2,
                                     float* __restrict__ lse2, int splits, int B, int Hq, int S) {
   constexpr int V = D / 32;
+  pdl_launch_dependents();
+  pdl_wait();
   const long long rows = static_cast<long long>(B) * Hq * S;
   const int lane = threadIdx.x & 31;
   for (long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows;
@@ -612,14 +616,15 @@ int launch_one(const Attn2Params& p, dim3 grid, int num_sms, cudaStream_t stream
       return TB200_ERR_CUDA;
     attr_set[dev & 31] = true;
   }
-  attn_fwd2_kernel<T, D><<<grid, kThreads, Smem2<D>::kTotal, stream>>>(p);
+  if (launch_chained(attn_fwd2_kernel<T, D>, grid, dim3(kThreads, 1, 1), Smem2<D>::kTotal, stream, p) != cudaSuccess) return TB200_ERR_CUDA;
   if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
   if (p.kv_splits > 1) {
     const long long rows = static_cast<long long>(p.B) * p.Hq * p.S;
     long long blocks = (rows * 32 + 255) / 256;
     if (blocks > num_sms * 8) blocks = num_sms * 8;
-    attn_combine_kernel<T, D><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.part_o, p.part_ml, static_cast<T*>(p.o2), p.lse2,
-                                                                             p.kv_splits, p.B, p.Hq, p.S);
+    if (launch_chained(attn_combine_kernel<T, D>, dim3(static_cast<unsigned>(blocks), 1, 1), dim3(256, 1, 1), 0, stream, p.part_o, p.part_ml,
+                       static_cast<T*>(p.o2), p.lse2, p.kv_splits, p.B, p.Hq, p.S) != cudaSuccess)
+      return TB200_ERR_CUDA;
     if (cudaGetLastError() != cudaSuccess) return TB200_ERR_CUDA;
   }
   return TB200_OK;

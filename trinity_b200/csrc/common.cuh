@@ -117,6 +117,30 @@ __device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp
 // all committed stores of this thread are complete
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialisation may start while the
+// kernel before it in the stream still runs: what it does before pdl_wait() (barrier and TMEM set-up, descriptor
+// prefetch, loads of tensors no kernel of the same call writes) overlaps that kernel's tail; pdl_wait() returns when
+// the earlier kernel has completed and its writes are visible.  pdl_launch_dependents() lets the NEXT kernel of the
+// stream start likewise.  Both are no-ops in a kernel launched the ordinary way.  Every thread of such a kernel
+// executes pdl_wait() before its first access to memory another kernel writes, so that a kernel never completes
+// before its predecessor has.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#ifdef TB200_TRACE
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// slot i: earliest, slot i + 1: latest
+__device__ __forceinline__ void trace_mark(unsigned long long* tr, int i) {
+  const unsigned long long t = trace_now();
+  atomicMin(tr + i, t);
+  atomicMax(tr + i + 1, t);
+}
+#endif
+
 // Barrier among `count` threads (a multiple of 32) of a CTA; id 0 is __syncthreads' own.
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

@@ -86,6 +86,9 @@ struct GemmParams {
   float* partial;
   long long ldp;
   int world, rank, rows_per_rank;
+#ifdef TB200_TRACE
+  int trace_slot;
+#endif
   CUtensorMap map_peer[kMaxPeers];   // GEMM_PEER: this rank's slot of every rank's staging buffer, (rows_per_rank, N)
   unsigned* peer_counter[kMaxPeers];
 };
@@ -131,7 +134,9 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u, int rank
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+// x * sigmoid(x) with the approximate exponential and reciprocal (a few ulp, far inside a 16-bit result): the exact
+// division is a twenty-instruction sequence, and with one tile per CTA (few-token FFN) nothing hides the epilogue.
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 template <typename T>
 __device__ __forceinline__ void store32(T* dst, const float (&v)[32]) {
@@ -154,8 +159,18 @@ __device__ __forceinline__ void store32_clipped(T* dst, const float (&v)[32], in
   }
 }
 
+#ifdef TB200_TRACE
+// per launch slot (8 slots): CTA start, producer past its wait, epilogue of the last unit done, CTA end -- earliest / latest
+static __device__ unsigned long long g_trace_gemm[64];
+static __device__ unsigned long long g_trace_fin[32];   // finish kernels, 8 slots: start, end
+static int g_trace_slot = 0, g_trace_fin_slot = 0;
+#define TRACE_GEMM(i) do { if ((threadIdx.x & 31) == 0) trace_mark(g_trace_gemm + 8 * p.trace_slot, i); } while (0)
+#else
+#define TRACE_GEMM(i)
+#endif
 template <typename T, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  if (threadIdx.x == 0) TRACE_GEMM(0);
   constexpr int NST = PAIR ? kStagesPair : kStages;
   constexpr int NCH = PAIR ? 2 : 4;  // B boxes this CTA stages
   constexpr int SB = kABytes + NCH * kBChunkBytes;
@@ -168,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  pdl_launch_dependents();  // the next kernel of the stream waits for this one's completion before it reads or writes
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
@@ -206,41 +222,65 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // One lane issues the boxes of a stage: the weights' (B) when with_b, the activations' (A) when with_a.
+    auto issue = [&](const Unit& t, int kb, int stage, bool with_a, bool with_b) {
+      uint8_t* sa = smem + stage * SB;
+      uint8_t* sb = sa + kABytes;
+      if (PAIR) {
+        // both CTAs' boxes are counted on the leader's barrier; the leader announces the pair's bytes
+        const uint32_t fb = mapa_u32(smem_u32(&full[stage]), 0);
+        if (with_b) {
+          if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * SB);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            const int g = rank * NCH + c;  // box of the pair's 256-column B tile
+            int src = t.src, col = t.n0 + 64 * g;
+            if (MODE == GEMM_SWIGLU) { src = g >> 1; col = t.n0 + 64 * (g & 1); }
+            if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (g >> 1); col = 64 * (g & 1); }
+            tma_load_2d_pair(sb + c * kBChunkBytes, &p.map_b[src], fb, col, kb * BK);
+          }
+        }
+        if (with_a) tma_load_2d_pair(sa, &p.map_a, fb, kb * BK, t.m0);
+      } else {
+        if (with_b) {
+          mbar_arrive_expect_tx(&full[stage], SB);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            int src = t.src, col = t.n0 + 64 * c;
+            if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
+            if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (c >> 1); col = 64 * (c & 1); }
+            tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
+          }
+        }
+        if (with_a) tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
+      }
+    };
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // The weights are written by no kernel of the call this launch belongs to, so the first stages' B boxes are
+    // requested before the wait for the kernel before this one; A, which that kernel may still be writing, after.
+    int prefilled = 0;
+    if (unit0 < p.total_units) {
+      const Unit t = decode_unit<PAIR>(p, unit0, rank);
+      prefilled = min(NST, t.kb_end - t.kb_begin);
+      if (lane == 0)
+        for (int i = 0; i < prefilled; ++i) issue(t, t.kb_begin + i, i, false, true);
+      pdl_wait();
+      TRACE_GEMM(2);
+      if (lane == 0)
+        for (int i = 0; i < prefilled; ++i) issue(t, t.kb_begin + i, i, true, false);
+      __syncwarp();
+      stage = prefilled == NST ? 0 : prefilled;
+      phase = prefilled == NST ? 1 : 0;
+    } else {
+      pdl_wait();
+    }
     for (int u = unit0; ok && u < p.total_units; u += unit_step) {
       const Unit t = decode_unit<PAIR>(p, u, rank);
-      for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
+      for (int kb = t.kb_begin + (u == unit0 ? prefilled : 0); kb < t.kb_end; ++kb) {
         if (!wait_bar<PAIR>(&empty[stage], phase ^ 1, ctx, 101)) { ok = false; break; }
-        if (lane == 0) {
-          uint8_t* sa = smem + stage * SB;
-          uint8_t* sb = sa + kABytes;
-          if (PAIR) {
-            // both CTAs' boxes are counted on the leader's barrier; the leader announces the pair's bytes
-            const uint32_t fb = mapa_u32(smem_u32(&full[stage]), 0);
-            if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * SB);
-            tma_load_2d_pair(sa, &p.map_a, fb, kb * BK, t.m0);
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-              const int g = rank * NCH + c;  // box of the pair's 256-column B tile
-              int src = t.src, col = t.n0 + 64 * g;
-              if (MODE == GEMM_SWIGLU) { src = g >> 1; col = t.n0 + 64 * (g & 1); }
-              if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (g >> 1); col = 64 * (g & 1); }
-              tma_load_2d_pair(sb + c * kBChunkBytes, &p.map_b[src], fb, col, kb * BK);
-            }
-          } else {
-            mbar_arrive_expect_tx(&full[stage], SB);
-            tma_load_2d(sa, &p.map_a, &full[stage], kb * BK, t.m0);
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-              int src = t.src, col = t.n0 + 64 * c;
-              if (MODE == GEMM_SWIGLU) { src = c >> 1; col = t.n0 + 64 * (c & 1); }
-              if (MODE == GEMM_QKV && p.kv_merged && t.src == 1) { src = 1 + (c >> 1); col = 64 * (c & 1); }
-              tma_load_2d(sb + c * kBChunkBytes, &p.map_b[src], &full[stage], col, kb * BK);
-            }
-          }
-        }
+        if (lane == 0) issue(t, kb, stage, true, true);
         __syncwarp();
         if (++stage == NST) { stage = 0; phase ^= 1; }
       }
@@ -248,6 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   } else if (warp == 1 && rank == 0) {
     // ------------------------------------------------------------ MMA issuer (a pair's leader issues for both CTAs)
     constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, PAIR ? 2 * BM : BM, BN);
+    pdl_wait();
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
@@ -285,6 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    pdl_wait();
     int acc = 0;
     uint32_t acc_phase = 0;
     unsigned* peer_pending = nullptr;  // GEMM_PEER: the counter the last tile has yet to arrive on
@@ -489,6 +531,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (warp == 2) TRACE_GEMM(4);
     if (MODE == GEMM_PEER && warp == 2 && lane == 0) {
       tma_store_wait_all();
       if (peer_pending != nullptr) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_pending) : "memory");
@@ -502,11 +545,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
     else tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) TRACE_GEMM(6);
 }
+#ifdef TB200_TRACE
+}  // namespace
+}  // namespace tb200
+extern "C" int tb200_trace_gemm(unsigned long long* out, int reset) {   // out: 64 + 32 values
+  if (reset) {
+    unsigned long long init[64];
+    for (int i = 0; i < 64; ++i) init[i] = (i & 1) ? 0 : ~0ULL;
+    tb200::g_trace_slot = 0;
+    tb200::g_trace_fin_slot = 0;
+    if (cudaMemcpyToSymbol(tb200::g_trace_fin, init, 32 * 8) != cudaSuccess) return 1;
+    return cudaMemcpyToSymbol(tb200::g_trace_gemm, init, sizeof(init)) == cudaSuccess ? 0 : 1;
+  }
+  if (cudaMemcpyFromSymbol(out + 64, tb200::g_trace_fin, 32 * 8) != cudaSuccess) return 1;
+  return cudaMemcpyFromSymbol(out, tb200::g_trace_gemm, 64 * 8) == cudaSuccess ? 0 : 1;
+}
+namespace tb200 {
+namespace {
+#endif
 
 // ------------------------------------------------------------------ split-K finish
 template <typename T>
-__global__ void splitk_finish_kernel(SplitKFinish f) {
+__global__ void splitk_finish_kernel(SplitKFinish f, int trace_slot) {
+#ifdef TB200_TRACE
+  if (threadIdx.x == 0) trace_mark(g_trace_fin + 4 * trace_slot, 0);
+#endif
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int kBatch = 8;   // slices whose loads are in flight together: one slice at a time costs a trip to L2 each
   const int64_t groups_per_row = f.N / 8;
   const int64_t total = static_cast<int64_t>(f.M) * groups_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -514,13 +582,29 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
     const int64_t row = i / groups_per_row;
     const int col = static_cast<int>(i - row * groups_per_row) * 8;
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s = 0; s < f.split_k; ++s) {  // fixed order: deterministic
-      const float* p = f.partial + (static_cast<int64_t>(s) * f.M + row) * f.ldp + col;
-      const float4 x0 = *reinterpret_cast<const float4*>(p), x1 = *reinterpret_cast<const float4*>(p + 4);
-      a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
-      if (f.gated) {
-        const float4 y0 = *reinterpret_cast<const float4*>(p + f.N), y1 = *reinterpret_cast<const float4*>(p + f.N + 4);
-        b[0] += y0.x; b[1] += y0.y; b[2] += y0.z; b[3] += y0.w; b[4] += y1.x; b[5] += y1.y; b[6] += y1.z; b[7] += y1.w;
+    const float* p0 = f.partial + row * f.ldp + col;
+    const int64_t slice = static_cast<int64_t>(f.M) * f.ldp;
+    for (int s0 = 0; s0 < f.split_k; s0 += kBatch) {  // fixed order: deterministic
+      float4 x[kBatch][2], y[kBatch][2];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const bool on = s0 + j < f.split_k;
+        const float* p = p0 + (on ? s0 + j : 0) * slice;
+        x[j][0] = on ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        x[j][1] = on ? __ldcg(reinterpret_cast<const float4*>(p + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (f.gated) {
+          y[j][0] = on ? __ldcg(reinterpret_cast<const float4*>(p + f.N)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          y[j][1] = on ? __ldcg(reinterpret_cast<const float4*>(p + f.N + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        a[0] += x[j][0].x; a[1] += x[j][0].y; a[2] += x[j][0].z; a[3] += x[j][0].w;
+        a[4] += x[j][1].x; a[5] += x[j][1].y; a[6] += x[j][1].z; a[7] += x[j][1].w;
+        if (f.gated) {
+          b[0] += y[j][0].x; b[1] += y[j][0].y; b[2] += y[j][0].z; b[3] += y[j][0].w;
+          b[4] += y[j][1].x; b[5] += y[j][1].y; b[6] += y[j][1].z; b[7] += y[j][1].w;
+        }
       }
     }
     const float rs = f.row_scale ? f.row_scale[row] : 1.f;
@@ -548,14 +632,18 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
     *reinterpret_cast<uint4*>(static_cast<T*>(f.C) + row * f.ldc + col) =
         make_uint4(Pack2<T>::pack(v[0], v[1]), Pack2<T>::pack(v[2], v[3]), Pack2<T>::pack(v[4], v[5]), Pack2<T>::pack(v[6], v[7]));
   }
+#ifdef TB200_TRACE
+  if (threadIdx.x == 0) trace_mark(g_trace_fin + 4 * trace_slot, 2);
+#endif
 }
-
 
 // ------------------------------------------------------------------ split-K finish of a QKV projection
 // One warp per (token row, head of q | k | v): the lanes cover the head's D columns, sum the K slices in a fixed
 // order, apply the row scale and the optional per-head RMSNorm (warp reduction), and write to q / the caches.
 template <typename T, int D>
 __global__ void qkv_finish_kernel(QkvFinish f) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = D / 32;  // columns per lane
   const int heads = f.Hq + 2 * f.Hkv;
   const long long ldp = static_cast<long long>(heads) * D;
@@ -569,10 +657,19 @@ __global__ void qkv_finish_kernel(QkvFinish f) {
 #pragma unroll
     for (int i = 0; i < V; ++i) v[i] = 0.f;
     const float* src = f.partial + row * ldp + static_cast<long long>(slot) * D + lane * V;
-    for (int s = 0; s < f.split_k; ++s) {
-      const float* ps = src + static_cast<long long>(s) * f.M * ldp;
+    for (int s0 = 0; s0 < f.split_k; s0 += 8) {   // eight slices' loads in flight together; the order of the sum is fixed
+      float x[8][V];
 #pragma unroll
-      for (int i = 0; i < V; ++i) v[i] += ps[i];
+      for (int j = 0; j < 8; ++j) {
+        const bool on = s0 + j < f.split_k;
+        const float* ps = src + static_cast<long long>(on ? s0 + j : 0) * f.M * ldp;
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[j][i] = on ? __ldcg(ps + i) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[i] += x[j][i];
     }
     const float rs = f.row_scale ? f.row_scale[row] : 1.f;
 #pragma unroll
@@ -610,17 +707,17 @@ int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   constexpr int kSmem = MODE == GEMM_PEER ? kPeerSmemBytes : kSmemBytes;
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = stream;
+  cfg.attrs = attr;
   if (PAIR) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
   if (!attr_set[dev & 31]) {
@@ -639,6 +736,14 @@ int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
   if (PAIR) ctas = p.total_units * 2 < ctas ? p.total_units * 2 : ctas;
   else ctas = p.total_units < ctas ? p.total_units : ctas;
   cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  if (chain_next_launch()) {  // not the first kernel of the call: may start while the kernel before it drains
+    attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++cfg.numAttrs;
+  }
+#ifdef TB200_TRACE
+  const_cast<GemmParams&>(p).trace_slot = g_trace_slot++ & 7;
+#endif
   if (cudaLaunchKernelEx(&cfg, gemm_kernel<T, MODE, PAIR>, p) != cudaSuccess) return TB200_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
@@ -799,14 +904,16 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
   const int threads = 256;
   int64_t blocks = (total + threads - 1) / threads;
   if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
-  if (f.dtype == TB200_BF16) {
-    splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
-  } else if (f.dtype == TB200_F16) {
-    splitk_finish_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(f);
-  } else {
-    return TB200_ERR_UNSUPPORTED;
-  }
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  const dim3 grid(static_cast<unsigned>(blocks), 1, 1), block(threads, 1, 1);
+  cudaError_t e;
+  int trace_slot = 0;
+#ifdef TB200_TRACE
+  trace_slot = g_trace_fin_slot++ & 7;
+#endif
+  if (f.dtype == TB200_BF16) e = launch_chained(splitk_finish_kernel<__nv_bfloat16>, grid, block, 0, stream, f, trace_slot);
+  else if (f.dtype == TB200_F16) e = launch_chained(splitk_finish_kernel<__half>, grid, block, 0, stream, f, trace_slot);
+  else return TB200_ERR_UNSUPPORTED;
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
 int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream) {
@@ -819,17 +926,18 @@ int launch_qkv_finish(const QkvFinish& f, cudaStream_t stream) {
   const long long items = static_cast<long long>(f.M) * (f.Hq + 2 * f.Hkv);
   long long blocks = (items * 32 + 255) / 256;
   if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
-  const unsigned g = static_cast<unsigned>(blocks);
+  const dim3 grid(static_cast<unsigned>(blocks), 1, 1), block(256, 1, 1);
+  cudaError_t e;
   if (f.dtype == TB200_BF16) {
-    if (f.D == 128) qkv_finish_kernel<__nv_bfloat16, 128><<<g, 256, 0, stream>>>(f);
-    else qkv_finish_kernel<__nv_bfloat16, 64><<<g, 256, 0, stream>>>(f);
+    e = f.D == 128 ? launch_chained(qkv_finish_kernel<__nv_bfloat16, 128>, grid, block, 0, stream, f)
+                   : launch_chained(qkv_finish_kernel<__nv_bfloat16, 64>, grid, block, 0, stream, f);
   } else if (f.dtype == TB200_F16) {
-    if (f.D == 128) qkv_finish_kernel<__half, 128><<<g, 256, 0, stream>>>(f);
-    else qkv_finish_kernel<__half, 64><<<g, 256, 0, stream>>>(f);
+    e = f.D == 128 ? launch_chained(qkv_finish_kernel<__half, 128>, grid, block, 0, stream, f)
+                   : launch_chained(qkv_finish_kernel<__half, 64>, grid, block, 0, stream, f);
   } else {
     return TB200_ERR_UNSUPPORTED;
   }
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
 // ====================================================================================================
@@ -934,6 +1042,7 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
     const uint32_t box[2] = {64, BK};
     if ((status = make_tensor_map(&p.map_b[s], srcs[s], 2, dims, strides, box)) != TB200_OK) return status;
   }
+  ChainScope chain;   // the finish kernel may start while the slices drain; it waits for them before it reads
   status = (a->dtype == TB200_BF16) ? launch_typed<__nv_bfloat16, false>(p, GEMM_PARTIAL, st->num_sms, stream)
                                     : launch_typed<__half, false>(p, GEMM_PARTIAL, st->num_sms, stream);
   if (status != TB200_OK) return status;

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/trinity_b200.h"
 
@@ -34,6 +35,37 @@ long long wait_limit_cycles();
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---------------------------------------------------------------- chained launches (runtime.cu)
+// Within one call of the library the kernels after the first are launched with programmatic stream serialisation
+// (see pdl_wait in common.cuh): their set-up and their weight prefetch overlap the tail of the kernel before.  The
+// FIRST kernel of a call is launched the ordinary way, so that everything written before the call -- its arguments,
+// weights included -- is complete before any kernel of the call starts.  A ChainScope marks the extent of a call on
+// the calling thread; outside one, and with tb200_set_chained_launch(0), every launch is an ordinary one.
+struct ChainScope {
+  ChainScope();
+  ~ChainScope();
+};
+// Whether the launch about to be made may carry the attribute; marks the call's first launch as done.
+bool chain_next_launch();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (chain_next_launch()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+}
 
 // ---------------------------------------------------------------- rmsnorm.cu
 // mean_divisor: the sum of squares is divided by this instead of cols when > 0 (the reference's Falcon
@@ -152,6 +184,31 @@ int launch_attn_fwd_pingpong(const AttnLaunch& a, cudaStream_t stream);
 int attn_kv_splits(int B, int S, int Hq, int kv_len, int num_sms);
 // attn_kf.cu: the same kernel with the KeyFormer statistic (noise tiles by TMA; kv_len a multiple of 8)
 int launch_attn_fwd_keyformer(const AttnLaunch& a, cudaStream_t stream);
+
+// ---------------------------------------------------------------- attn_dec.cu
+// Decode-sized query blocks (S <= 16, no KeyFormer / RoCo statistic): one kernel takes the projection's K-slice sums
+// (or a finished q with the caches already appended), finishes q and the new k, v rows, appends them to the caches and
+// computes softmax(Q K^T) V with the key shares merged inside a cluster.
+struct AttnDecodeLaunch {
+  int dtype = TB200_BF16;
+  int B = 0, S = 0, Hq = 0, Hkv = 0, D = 0, past = 0, cache_len = 0;
+  int causal = 0;
+  float sm_scale = 1.f;
+  const void* q = nullptr;          // (B,Hq,S,D); exactly one of q / partial
+  const float* partial = nullptr;   // (split, B*S, (Hq + 2 Hkv) * D) fp32 K-slice sums of the QKV projection
+  int split = 1;
+  const float* row_scale = nullptr;
+  int qknorm = 0;
+  float qk_eps = 0.f;
+  const void* q_norm_weight = nullptr;
+  const void* k_norm_weight = nullptr;
+  void* k_cache = nullptr;
+  void* v_cache = nullptr;
+  void* o2 = nullptr;
+  float* lse2 = nullptr;            // optional
+};
+bool attn_decode_applies(int B, int S, int Hq, int D);
+int launch_attn_decode(const AttnDecodeLaunch& a, cudaStream_t stream);
 
 // ---------------------------------------------------------------- score.cu
 struct ScoreLaunch {

@@ -16,6 +16,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ weight,
                                                          T* __restrict__ y, float* __restrict__ inv_rms, int cols,
                                                          float eps, float divisor) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = cols >> 3;  // 8 elements per 16-byte vector
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
@@ -94,6 +96,8 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const T* __restrict__
 template <typename T>
 __global__ void __launch_bounds__(256) row_stats_kernel(const T* __restrict__ x, float* __restrict__ inv_rms, int64_t rows, int cols,
                                                          float eps, float divisor) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -181,27 +185,30 @@ int launch_rmsnorm(const void* x, const void* weight, void* y, float* inv_rms, i
     if (!st) return status;
     int64_t blocks = (rows + 7) / 8;
     if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
+    const dim3 sgrid(static_cast<unsigned>(blocks), 1, 1), sblock(256, 1, 1);
+    cudaError_t e;
     if (dtype == TB200_BF16)
-      row_stats_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), inv_rms, rows,
-                                                                                       static_cast<int>(cols), eps, divisor);
+      e = launch_chained(row_stats_kernel<__nv_bfloat16>, sgrid, sblock, 0, stream, static_cast<const __nv_bfloat16*>(x), inv_rms, rows,
+                         static_cast<int>(cols), eps, divisor);
     else if (dtype == TB200_F16)
-      row_stats_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __half*>(x), inv_rms, rows, static_cast<int>(cols),
-                                                                                eps, divisor);
+      e = launch_chained(row_stats_kernel<__half>, sgrid, sblock, 0, stream, static_cast<const __half*>(x), inv_rms, rows,
+                         static_cast<int>(cols), eps, divisor);
     else
       return TB200_ERR_UNSUPPORTED;
-    return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
   }
+  const dim3 block(kThreads, 1, 1);
+  cudaError_t e;
   if (dtype == TB200_BF16) {
-    rmsnorm_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                              static_cast<const __nv_bfloat16*>(weight),
-                                                              static_cast<__nv_bfloat16*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
+    e = launch_chained(rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, static_cast<const __nv_bfloat16*>(x),
+                       static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
   } else if (dtype == TB200_F16) {
-    rmsnorm_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(weight),
-                                                       static_cast<__half*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
+    e = launch_chained(rmsnorm_kernel<__half>, grid, block, 0, stream, static_cast<const __half*>(x), static_cast<const __half*>(weight),
+                       static_cast<__half*>(y), inv_rms, static_cast<int>(cols), eps, divisor);
   } else {
     return TB200_ERR_UNSUPPORTED;
   }
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
 }  // namespace tb200

@@ -19,11 +19,26 @@ bool g_ready[kMaxDevices];
 std::mutex g_mu;
 std::atomic<long long> g_wait_limit{4000000000LL};   // = kDefaultWaitLimitCycles of common.cuh
 
+std::atomic<int> g_chained{1};
+thread_local bool t_chain_active = false;
+thread_local bool t_chain_first = true;
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 }  // namespace
+
+ChainScope::ChainScope() {
+  t_chain_active = true;
+  t_chain_first = true;
+}
+ChainScope::~ChainScope() { t_chain_active = false; }
+bool chain_next_launch() {
+  const bool chained = t_chain_active && !t_chain_first && g_chained.load(std::memory_order_relaxed) != 0;
+  t_chain_first = false;
+  return chained;
+}
 
 DeviceState* device_state(int* status) {
   int dev = -1;
@@ -143,6 +158,8 @@ int tb200_set_wait_limit_cycles(long long cycles) {
 }
 
 long long tb200_get_wait_limit_cycles(void) { return tb200::wait_limit_cycles(); }
+
+int tb200_set_chained_launch(int enabled) { return tb200::g_chained.exchange(enabled ? 1 : 0, std::memory_order_relaxed); }
 
 int tb200_selftest_wait_timeout(long long limit_cycles, void* stream) {
   if (limit_cycles < 1000 || limit_cycles > 2000000000LL) return TB200_ERR_INVALID;   // at most about a second
