@@ -257,6 +257,15 @@ size_t tb200_ffn_workspace_bytes(const tb200_ffn_args* args);
 int tb200_ffn_forward(const tb200_ffn_args* args, void* stream);
 /* The host-side argument checks of tb200_ffn_forward alone (workspace excepted): nothing is launched. */
 int tb200_ffn_check(const tb200_ffn_args* args);
+/* tb200_attn_forward(attn) followed by tb200_ffn_forward(ffn) as ONE call: the FFN block must consume the attention
+ * block's output (ffn->o2 == attn->o2, ffn->wo given, tokens = batch * seq, equal dtype and hidden size).  The
+ * two blocks form one launch chain (tb200_set_chained_launch): the output projection is launched while the
+ * attention kernel drains and has its first weight tiles in flight when o2 is complete.  Results are those of the
+ * two separate calls, bit for bit.  Every argument check of both blocks is made before the first launch.
+ * Replaces the reference's pair of generated modules run back to back (the attention module of
+ * evaluation/prenorm/prenorm_falcon_benchmark579.py:115-120 feeding the FFN module of
+ * evaluation/ffn/ffn_llama/ffn_llama_benchmark2248.py:45-62). */
+int tb200_layer_forward(const tb200_attn_args* attn, const tb200_ffn_args* ffn, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Deterministic top-k over the last axis of scores (rows, n) fp32: idx[r,:] = the first k entries of

@@ -118,3 +118,95 @@ def test_ffn_block_with_a_weighted_norm():
     f = lambda k: t[k].float()
     ref = orc.ffn_block(f("O2"), f("WFF1b"), f("WFF1a"), f("WFF2"), wo=f("WO"), residual=f("X"), norm=True, norm_weight=f("g"), norm_eps=1e-5)
     close(ff2, ref["FF2"], rtol=3e-2, atol=3e-2 * float(ref["FF2"].abs().max()), msg="FF2")
+
+
+def _layer_case(B, S, N, Hq, Hkv, D, P, inner, dt, flags):
+    g = torch.Generator().manual_seed(11)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    t = dict(x=rn(B, S, N), wq=rn(N, Hq * D) * 0.02, wk=rn(N, Hkv * D) * 0.02, wv=rn(N, Hkv * D) * 0.02,
+             kc=rn(B, Hkv, P + S, D), vc=rn(B, Hkv, P + S, D), wo=rn(N, N) * 0.02, nw=1 + 0.02 * rn(N),
+             wg=rn(N, inner) * 0.02, wu=rn(N, inner) * 0.02, wd=rn(inner, N) * 0.02)
+    return {k: v.to(dt).to(dev()) for k, v in t.items()}
+
+
+@pytest.mark.parametrize("B,S,N,Hq,Hkv,D,P,inner,dt", [
+    (1, 16, 1024, 8, 2, 128, 1000, 2816, torch.float16),      # decode-sized: sliced projections, one-kernel attention
+    (2, 200, 512, 8, 8, 64, 56, 1408, torch.bfloat16),        # prefill-sized: tile-parallel projections
+])
+def test_layer_call_equals_the_two_block_calls(B, S, N, Hq, Hkv, D, P, inner, dt):
+    """tb200_layer_forward = tb200_attn_forward + tb200_ffn_forward, bit for bit, with chained launches on and off, in
+    eager mode and replayed from a CUDA graph; and the pair agrees with the oracle."""
+    lib = L.load()
+    flags = L.ATTN_CAUSAL | L.ATTN_PRENORM
+    t = _layer_case(B, S, N, Hq, Hkv, D, P, inner, dt, flags)
+
+    def buffers():
+        return dict(kc=t["kc"].clone(), vc=t["vc"].clone(), o2=torch.full((B, S, N), float("nan"), dtype=dt, device=dev()),
+                    ff2=torch.full((B * S, N), float("nan"), dtype=dt, device=dev()))
+
+    def attn_kw(b):
+        return dict(tensors=(t["x"], t["wq"], t["wk"], t["wv"], b["kc"], b["vc"], b["o2"]), past=P, head_dim=D, flags=flags,
+                    sm_scale=D ** -0.5, norm_weight=t["nw"], norm_eps=1e-5)
+
+    def ffn_kw(b):
+        return dict(tensors=(t["x"].view(B * S, N), t["wg"], t["wu"], t["wd"], b["ff2"]), act=L.FFN_SWIGLU, flags=L.FFN_NORM,
+                    o2=b["o2"].view(B * S, N), wo=t["wo"], norm_weight=t["nw"], norm_eps=1e-5)
+
+    def separate(b):
+        a, f = attn_kw(b), ffn_kw(b)
+        ops.attn_forward(*a.pop("tensors"), **a)
+        ops.ffn_forward(*f.pop("tensors"), **f)
+
+    results = []
+    try:
+        for chained in (0, 1):
+            lib.tb200_set_chained_launch(chained)
+            for run in (separate, lambda b: ops.layer_forward(attn_kw(b), ffn_kw(b))):
+                b = buffers()
+                run(b)
+                assert ops.device_status() == 0
+                results.append(b)
+        lib.tb200_set_chained_launch(1)
+        b = buffers()
+        ops.layer_forward(attn_kw(b), ffn_kw(b))          # warm-up: workspaces and folded weights exist before capture
+        torch.cuda.synchronize()
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                ops.layer_forward(attn_kw(b), ffn_kw(b))
+        for name in ("o2", "ff2"):
+            b[name].fill_(float("nan"))
+        b["kc"].copy_(t["kc"]); b["vc"].copy_(t["vc"])
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        results.append(b)
+    finally:
+        lib.tb200_set_chained_launch(1)
+    first = results[0]
+    for other in results[1:]:
+        for name in ("o2", "ff2", "kc", "vc"):
+            assert torch.equal(first[name], other[name]), f"{name} differs between the ways of launching the same work"
+    # against the oracle: the attention block, then the FFN block on its output
+    f32 = lambda v: v.float().cpu()
+    ref_a = orc.attention_block(f32(t["x"]), f32(t["wq"]), f32(t["wk"]), f32(t["wv"]), f32(t["kc"]), f32(t["vc"]), past=P, head_dim=D,
+                                prenorm=True, norm_weight=f32(t["nw"]), norm_eps=1e-5, causal=True, sm_scale=D ** -0.5)
+    close(first["o2"], ref_a["O2"], msg="O2 of the layer call")
+    ref_f = orc.ffn_block(f32(first["o2"]).view(B * S, N), f32(t["wg"]), f32(t["wu"]), f32(t["wd"]), wo=f32(t["wo"]),
+                          residual=f32(t["x"]).view(B * S, N), norm=True, norm_weight=f32(t["nw"]), norm_eps=1e-5)
+    close(first["ff2"], ref_f["FF2"], msg="FF2 of the layer call")
+
+
+def test_layer_call_refuses_blocks_that_do_not_fit_together():
+    lib = L.load()
+    t = _layer_case(1, 16, 256, 2, 2, 128, 0, 512, torch.bfloat16, 0)
+    o2 = torch.empty(1, 16, 256, dtype=torch.bfloat16, device=dev())
+    other = torch.empty(16, 256, dtype=torch.bfloat16, device=dev())
+    ff2 = torch.empty(16, 256, dtype=torch.bfloat16, device=dev())
+    attn = dict(tensors=(t["x"], t["wq"], t["wk"], t["wv"], t["kc"], t["vc"], o2), past=0, head_dim=128)
+    with pytest.raises(L.Tb200Error):      # the FFN reads another tensor than the attention block writes
+        ops.layer_forward(attn, dict(tensors=(t["x"].view(16, 256), t["wg"], t["wu"], t["wd"], ff2), o2=other, wo=t["wo"]))
+    with pytest.raises(L.Tb200Error):      # an FFN without the output projection does not consume o2 at all
+        ops.layer_forward(attn, dict(tensors=(t["x"].view(16, 256), t["wg"], t["wu"], t["wd"], ff2)))
+    assert ops.device_status() == 0

@@ -99,6 +99,7 @@ SYMBOLS = {
     "tb200_attn_forward_timed": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.POINTER(C.c_float)]),
     "tb200_ffn_workspace_bytes": (C.c_size_t, [C.POINTER(FfnArgs)]),
     "tb200_ffn_forward": (C.c_int, [C.POINTER(FfnArgs), C.c_void_p]),
+    "tb200_layer_forward": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(FfnArgs), C.c_void_p]),
     "tb200_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "tb200_kv_compact_max_keep": (C.c_int64, [C.POINTER(KvCompactArgs)]),
     "tb200_kv_compact": (C.c_int, [C.POINTER(KvCompactArgs), C.c_void_p]),

@@ -520,4 +520,25 @@ int tb200_ffn_forward(const tb200_ffn_args* a, void* stream_) {
   return launch_rmsnorm(w.o_ff, nullptr, a->o_ff_norm, nullptr, M, N, 0.f, a->dtype, stream, a->tail_divisor);
 }
 
+// The attention block and the FFN block that consumes its o2, as one launch chain: the FFN's first projection is
+// launched while the attention kernel still runs, sets up and requests its first weight boxes, and waits for o2.
+// Everything either block would refuse is refused here before the first launch.
+int tb200_layer_forward(const tb200_attn_args* attn, const tb200_ffn_args* ffn, void* stream) {
+  int status = TB200_OK;
+  DeviceState* st = device_state(&status);
+  if (!st) return status;
+  if ((status = check_attn(attn)) != TB200_OK) return status;
+  if ((status = check_ffn(ffn)) != TB200_OK) return status;
+  if (ffn->o2 == nullptr || ffn->o2 != attn->o2 || ffn->dtype != attn->dtype || ffn->hidden != attn->hidden ||
+      ffn->tokens != static_cast<int64_t>(attn->batch) * attn->seq || attn->n_q_heads * attn->head_dim != attn->hidden)
+    return TB200_ERR_INVALID;
+  if (attn->workspace == nullptr || !aligned16(attn->workspace) || attn->workspace_bytes < carve_attn(attn, nullptr, st->num_sms).bytes)
+    return TB200_ERR_WORKSPACE;
+  const size_t ffn_need = carve_ffn(ffn, nullptr, st->num_sms).bytes;
+  if (ffn_need > 0 && (ffn->workspace == nullptr || !aligned16(ffn->workspace) || ffn->workspace_bytes < ffn_need)) return TB200_ERR_WORKSPACE;
+  ChainScope chain;
+  if ((status = attn_forward_impl(attn, stream, nullptr)) != TB200_OK) return status;
+  return tb200_ffn_forward(ffn, stream);
+}
+
 }  // extern "C"

@@ -103,7 +103,9 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // The cluster's barrier in its two halves; every thread of every CTA executes both, in this order, once per phase.
+// The relaxed arrival publishes nothing (it only says "I am here"), so it does not wait for this thread's stores.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ float2 ld_cluster_f32x2(uint32_t cluster_addr) {
   float2 v;
@@ -283,12 +285,6 @@ __device__ __forceinline__ void chunk_step(const uint32_t (&qf)[D / 16][4], uint
   }
 }
 
-#ifdef TB200_TRACE
-static __device__ unsigned long long g_trace_dec[16];
-#define TRACE_DEC(i) do { if (threadIdx.x == 0) trace_mark(g_trace_dec, i); } while (0)
-#else
-#define TRACE_DEC(i)
-#endif
 
 // C: CTAs per cluster = shares of the cached keys per (batch, q head).
 template <typename T, int D, int C>
@@ -297,10 +293,9 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
   constexpr int kRow = L::kRow;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  TRACE_DEC(0);
   pdl_launch_dependents();
   const bool from_partial = p.partial != nullptr;
-  if (from_partial) cluster_arrive();   // "this CTA runs": a peer may write its shared memory after waiting for this
+  if (from_partial) cluster_arrive_relaxed();   // "this CTA runs": a peer may write its shared memory after waiting for this
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int share = static_cast<int>(blockIdx.x) % C;   // = rank in the cluster
@@ -355,7 +350,6 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
     }
   }
   if (from_partial) pdl_wait();   // the K-slice sums come from the kernel before this one
-  TRACE_DEC(2);
 
   // ---- q (and this CTA's part of the new k, v rows) out of the K-slice sums, or q as the projection left it
   if (from_partial) {
@@ -394,13 +388,15 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
         const uint32_t dst = chunk + L::piece_offset(kv_row, col >> 3) + (col & 4) * 2;
         asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(w[2 * i]), "r"(w[2 * i + 1]) : "memory");
       }
+      cluster_arrive();   // "my rows are written"; waited for below.  Before the cache append: the arrival must not wait for it
       if (kv_live && hq == hkv * group) {
         uint2* dg = reinterpret_cast<uint2*>((is_v ? vc : kc) + static_cast<long long>(p.past + kv_row) * D + kv_c0);
 #pragma unroll
         for (int i = 0; i < kKvCpt / 4; ++i) dg[i] = make_uint2(w[2 * i], w[2 * i + 1]);
       }
+    } else {
+      cluster_arrive();
     }
-    cluster_arrive();   // "my rows are written"; waited for below
   } else {
     const T* q = static_cast<const T*>(p.q) + (static_cast<long long>(b) * p.Hq + hq) * p.S * D;
     constexpr int kVecs = D / 8;
@@ -412,7 +408,6 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
     }
   }
   __syncthreads();
-  TRACE_DEC(4);
 
   uint32_t qf[D / 16][4];
   {  // A fragments of Q: matrices (rows 0-7, d 0-7), (rows 8-15, d 0-7), (rows 0-7, d 8-15), (rows 8-15, d 8-15)
@@ -451,7 +446,6 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
       chunk_step<T, D>(qf, kbase, kbase + L::kChunkBytes, p.past, p.S, p, m, l, o);
     }
   }
-  TRACE_DEC(6);
 
   // ---- merge the warps
 #pragma unroll
@@ -512,7 +506,6 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
   //      remote loads of an output pair are independent: one trip through the cluster's network, not one per share.
   cluster_arrive();
   cluster_wait();
-  TRACE_DEC(8);
   {
     constexpr int kCols = D / C, kPairs = kCols / 2;
     const uint32_t o_local = smem_u32(smem + L::kCtaO), ml_local = smem_u32(smem + L::kCtaML);
@@ -543,24 +536,9 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const __grid_c
       if (p.lse2 != nullptr && col == 0) p.lse2[(static_cast<long long>(b) * p.Hq + hq) * p.S + row] = mm + log2f(ll);
     }
   }
-  cluster_arrive();   // nobody's shared memory goes away while a peer still reads it
+  cluster_arrive_relaxed();   // nobody's shared memory goes away while a peer still reads it
   cluster_wait();
-  TRACE_DEC(10);
 }
-#ifdef TB200_TRACE
-}  // namespace
-}  // namespace tb200
-extern "C" int tb200_trace_dec(unsigned long long* out16, int reset) {
-  if (reset) {
-    unsigned long long init[16];
-    for (int i = 0; i < 16; ++i) init[i] = (i & 1) ? 0 : ~0ULL;
-    return cudaMemcpyToSymbol(tb200::g_trace_dec, init, sizeof(init)) == cudaSuccess ? 0 : 1;
-  }
-  return cudaMemcpyFromSymbol(out16, tb200::g_trace_dec, 128) == cudaSuccess ? 0 : 1;
-}
-namespace tb200 {
-namespace {
-#endif
 
 template <typename T, int D, int C>
 int launch_one(const DecodeParams& p, cudaStream_t stream) {

@@ -127,19 +127,6 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-#ifdef TB200_TRACE
-__device__ __forceinline__ unsigned long long trace_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// slot i: earliest, slot i + 1: latest
-__device__ __forceinline__ void trace_mark(unsigned long long* tr, int i) {
-  const unsigned long long t = trace_now();
-  atomicMin(tr + i, t);
-  atomicMax(tr + i + 1, t);
-}
-#endif
 
 // Barrier among `count` threads (a multiple of 32) of a CTA; id 0 is __syncthreads' own.
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {

@@ -86,9 +86,6 @@ struct GemmParams {
   float* partial;
   long long ldp;
   int world, rank, rows_per_rank;
-#ifdef TB200_TRACE
-  int trace_slot;
-#endif
   CUtensorMap map_peer[kMaxPeers];   // GEMM_PEER: this rank's slot of every rank's staging buffer, (rows_per_rank, N)
   unsigned* peer_counter[kMaxPeers];
 };
@@ -159,18 +156,8 @@ __device__ __forceinline__ void store32_clipped(T* dst, const float (&v)[32], in
   }
 }
 
-#ifdef TB200_TRACE
-// per launch slot (8 slots): CTA start, producer past its wait, epilogue of the last unit done, CTA end -- earliest / latest
-static __device__ unsigned long long g_trace_gemm[64];
-static __device__ unsigned long long g_trace_fin[32];   // finish kernels, 8 slots: start, end
-static int g_trace_slot = 0, g_trace_fin_slot = 0;
-#define TRACE_GEMM(i) do { if ((threadIdx.x & 31) == 0) trace_mark(g_trace_gemm + 8 * p.trace_slot, i); } while (0)
-#else
-#define TRACE_GEMM(i)
-#endif
 template <typename T, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
-  if (threadIdx.x == 0) TRACE_GEMM(0);
   constexpr int NST = PAIR ? kStagesPair : kStages;
   constexpr int NCH = PAIR ? 2 : 4;  // B boxes this CTA stages
   constexpr int SB = kABytes + NCH * kBChunkBytes;
@@ -267,7 +254,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       if (lane == 0)
         for (int i = 0; i < prefilled; ++i) issue(t, t.kb_begin + i, i, false, true);
       pdl_wait();
-      TRACE_GEMM(2);
       if (lane == 0)
         for (int i = 0; i < prefilled; ++i) issue(t, t.kb_begin + i, i, true, false);
       __syncwarp();
@@ -531,7 +517,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (warp == 2) TRACE_GEMM(4);
     if (MODE == GEMM_PEER && warp == 2 && lane == 0) {
       tma_store_wait_all();
       if (peer_pending != nullptr) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_pending) : "memory");
@@ -545,33 +530,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
     else tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 0) TRACE_GEMM(6);
 }
-#ifdef TB200_TRACE
-}  // namespace
-}  // namespace tb200
-extern "C" int tb200_trace_gemm(unsigned long long* out, int reset) {   // out: 64 + 32 values
-  if (reset) {
-    unsigned long long init[64];
-    for (int i = 0; i < 64; ++i) init[i] = (i & 1) ? 0 : ~0ULL;
-    tb200::g_trace_slot = 0;
-    tb200::g_trace_fin_slot = 0;
-    if (cudaMemcpyToSymbol(tb200::g_trace_fin, init, 32 * 8) != cudaSuccess) return 1;
-    return cudaMemcpyToSymbol(tb200::g_trace_gemm, init, sizeof(init)) == cudaSuccess ? 0 : 1;
-  }
-  if (cudaMemcpyFromSymbol(out + 64, tb200::g_trace_fin, 32 * 8) != cudaSuccess) return 1;
-  return cudaMemcpyFromSymbol(out, tb200::g_trace_gemm, 64 * 8) == cudaSuccess ? 0 : 1;
-}
-namespace tb200 {
-namespace {
-#endif
 
 // ------------------------------------------------------------------ split-K finish
 template <typename T>
-__global__ void splitk_finish_kernel(SplitKFinish f, int trace_slot) {
-#ifdef TB200_TRACE
-  if (threadIdx.x == 0) trace_mark(g_trace_fin + 4 * trace_slot, 0);
-#endif
+__global__ void splitk_finish_kernel(SplitKFinish f) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int kBatch = 8;   // slices whose loads are in flight together: one slice at a time costs a trip to L2 each
@@ -632,9 +595,6 @@ __global__ void splitk_finish_kernel(SplitKFinish f, int trace_slot) {
     *reinterpret_cast<uint4*>(static_cast<T*>(f.C) + row * f.ldc + col) =
         make_uint4(Pack2<T>::pack(v[0], v[1]), Pack2<T>::pack(v[2], v[3]), Pack2<T>::pack(v[4], v[5]), Pack2<T>::pack(v[6], v[7]));
   }
-#ifdef TB200_TRACE
-  if (threadIdx.x == 0) trace_mark(g_trace_fin + 4 * trace_slot, 2);
-#endif
 }
 
 // ------------------------------------------------------------------ split-K finish of a QKV projection
@@ -741,9 +701,6 @@ int launch_mode(const GemmParams& p, int slots, cudaStream_t stream) {
     attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
     ++cfg.numAttrs;
   }
-#ifdef TB200_TRACE
-  const_cast<GemmParams&>(p).trace_slot = g_trace_slot++ & 7;
-#endif
   if (cudaLaunchKernelEx(&cfg, gemm_kernel<T, MODE, PAIR>, p) != cudaSuccess) return TB200_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
@@ -906,12 +863,8 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
   if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
   const dim3 grid(static_cast<unsigned>(blocks), 1, 1), block(threads, 1, 1);
   cudaError_t e;
-  int trace_slot = 0;
-#ifdef TB200_TRACE
-  trace_slot = g_trace_fin_slot++ & 7;
-#endif
-  if (f.dtype == TB200_BF16) e = launch_chained(splitk_finish_kernel<__nv_bfloat16>, grid, block, 0, stream, f, trace_slot);
-  else if (f.dtype == TB200_F16) e = launch_chained(splitk_finish_kernel<__half>, grid, block, 0, stream, f, trace_slot);
+  if (f.dtype == TB200_BF16) e = launch_chained(splitk_finish_kernel<__nv_bfloat16>, grid, block, 0, stream, f);
+  else if (f.dtype == TB200_F16) e = launch_chained(splitk_finish_kernel<__half>, grid, block, 0, stream, f);
   else return TB200_ERR_UNSUPPORTED;
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }

@@ -20,7 +20,7 @@ std::mutex g_mu;
 std::atomic<long long> g_wait_limit{4000000000LL};   // = kDefaultWaitLimitCycles of common.cuh
 
 std::atomic<int> g_chained{1};
-thread_local bool t_chain_active = false;
+thread_local int t_chain_depth = 0;      // ChainScopes open on this thread (a call may be made of calls)
 thread_local bool t_chain_first = true;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -30,12 +30,11 @@ EncodeTiledFn g_encode = nullptr;
 }  // namespace
 
 ChainScope::ChainScope() {
-  t_chain_active = true;
-  t_chain_first = true;
+  if (t_chain_depth++ == 0) t_chain_first = true;   // only the outermost scope starts a chain
 }
-ChainScope::~ChainScope() { t_chain_active = false; }
+ChainScope::~ChainScope() { --t_chain_depth; }
 bool chain_next_launch() {
-  const bool chained = t_chain_active && !t_chain_first && g_chained.load(std::memory_order_relaxed) != 0;
+  const bool chained = t_chain_depth > 0 && !t_chain_first && g_chained.load(std::memory_order_relaxed) != 0;
   t_chain_first = false;
   return chained;
 }

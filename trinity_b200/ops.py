@@ -158,12 +158,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, b2: Optional[torch.Tensor] = None,
     return out
 
 
-def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: int, flags: int = 0,
-                 sm_scale: float = 1.0, norm_weight=None, norm_eps: float = 0.0, q_norm_weight=None,
-                 k_norm_weight=None, qk_eps: float = 0.0, noise=None, tau: float = 1.5, c_out=None,
-                 c_out1=None, c_out2=None, topk: int = 0, topk_idx=None, timed: bool = False):
-    """The fused attention block; mutates ``o2``, the cache rows ``[past, past+S)`` and the c_out* tensors.
-    With ``timed`` the call waits for the stream and returns the four stage durations in ms."""
+def _attn_args(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: int, flags: int = 0,
+               sm_scale: float = 1.0, norm_weight=None, norm_eps: float = 0.0, q_norm_weight=None,
+               k_norm_weight=None, qk_eps: float = 0.0, noise=None, tau: float = 1.5, c_out=None,
+               c_out1=None, c_out2=None, topk: int = 0, topk_idx=None):
+    """The argument block of tb200_attn_forward with its workspace attached.  Returns (args, tensors to keep alive)."""
     lib = L.load()
     if x.dim() == 2:
         batch, (seq, hidden) = 1, x.shape
@@ -190,6 +189,15 @@ def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: in
         raise L.Tb200Error(-1, "tb200_attn_workspace_bytes")
     ws = Workspace.get(x.device, need, "attn")
     args.workspace, args.workspace_bytes = _ptr(ws), need
+    return args, (wq, wk, wv, ws)
+
+
+def attn_forward(*tensors, timed: bool = False, **kw):
+    """The fused attention block: ``attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, past=, head_dim=, flags=, ...)``;
+    mutates ``o2``, the cache rows ``[past, past+S)`` and the c_out* tensors.  With ``timed`` the call waits for the
+    stream and returns the four stage durations in ms."""
+    lib = L.load()
+    args, _keep = _attn_args(*tensors, **kw)
     if timed:
         ms = (C.c_float * 4)()
         L.check(lib.tb200_attn_forward_timed(C.byref(args), _stream(), ms), "tb200_attn_forward_timed")
@@ -197,10 +205,10 @@ def attn_forward(x, wq, wk, wv, k_cache, v_cache, o2, *, past: int, head_dim: in
     L.check(lib.tb200_attn_forward(C.byref(args), _stream()), "tb200_attn_forward")
 
 
-def ffn_forward(x, w_gate, w_up, w_down, ff2, *, act: int = L.FFN_SWIGLU, flags: int = 0, o2=None, wo=None,
-                norm_weight=None, norm_eps: float = 0.0, tail_divisor: int = 0, attn_o2=None, ff1=None,
-                o_ff_norm=None) -> None:
-    """The fused FFN block; mutates ``ff2`` (and ``attn_o2`` / ``ff1`` / ``o_ff_norm`` when given)."""
+def _ffn_args(x, w_gate, w_up, w_down, ff2, *, act: int = L.FFN_SWIGLU, flags: int = 0, o2=None, wo=None,
+              norm_weight=None, norm_eps: float = 0.0, tail_divisor: int = 0, attn_o2=None, ff1=None,
+              o_ff_norm=None):
+    """The argument block of tb200_ffn_forward with its workspace attached.  Returns (args, tensors to keep alive)."""
     lib = L.load()
     hidden = x.shape[-1]
     tokens = x.numel() // hidden
@@ -217,7 +225,24 @@ def ffn_forward(x, w_gate, w_up, w_down, ff2, *, act: int = L.FFN_SWIGLU, flags:
     need = lib.tb200_ffn_workspace_bytes(C.byref(args))
     ws = Workspace.get(x.device, need, "ffn")
     args.workspace, args.workspace_bytes = _ptr(ws), need
-    L.check(lib.tb200_ffn_forward(C.byref(args), _stream()), "tb200_ffn_forward")
+    return args, (w_gate, w_up, ws)
+
+
+def ffn_forward(*tensors, **kw) -> None:
+    """The fused FFN block: ``ffn_forward(x, w_gate, w_up, w_down, ff2, act=, flags=, o2=, wo=, ...)``; mutates ``ff2``
+    (and ``attn_o2`` / ``ff1`` / ``o_ff_norm`` when given)."""
+    args, _keep = _ffn_args(*tensors, **kw)
+    L.check(L.load().tb200_ffn_forward(C.byref(args), _stream()), "tb200_ffn_forward")
+
+
+def layer_forward(attn: dict, ffn: dict) -> None:
+    """The attention block and the FFN block that consumes its ``o2`` as ONE call (tb200_layer_forward): one launch chain,
+    in which the FFN's first projection starts its weight stream while the attention kernel drains.  ``attn`` and ``ffn``
+    hold the arguments of ``attn_forward`` / ``ffn_forward`` (positional tensors under the key ``"tensors"``); the FFN's
+    ``o2`` must be the attention block's."""
+    a_args, _ka = _attn_args(*attn["tensors"], **{k: v for k, v in attn.items() if k != "tensors"})
+    f_args, _kf = _ffn_args(*ffn["tensors"], **{k: v for k, v in ffn.items() if k != "tensors"})
+    L.check(L.load().tb200_layer_forward(C.byref(a_args), C.byref(f_args), _stream()), "tb200_layer_forward")
 
 
 def topk(scores: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
