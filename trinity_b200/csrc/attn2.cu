@@ -582,18 +582,30 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   const int lane = threadIdx.x & 31;
   for (long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows;
        row += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    // all the shares' loads are in flight together (at most 16 shares): one trip to L2, not one per share
+    constexpr int kMaxSplits = 16;
+    float2 ml[kMaxSplits];
+    float po[kMaxSplits][V];
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; ++s) {
+      const bool on = s < splits;
+      ml[s] = on ? __ldcg(reinterpret_cast<const float2*>(part_ml + (s * rows + row) * 2)) : make_float2(-INFINITY, 0.f);
+      const float* ps = part_o + ((on ? s : 0) * rows + row) * D + lane * V;
+#pragma unroll
+      for (int i = 0; i < V; ++i) po[s][i] = on ? __ldcg(ps + i) : 0.f;
+    }
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(s * rows + row) * 2]);
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; ++s) m = fmaxf(m, ml[s].x);
     float l = 0.f, acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
-    for (int s = 0; s < splits; ++s) {  // fixed order: deterministic
-      const float ms = part_ml[(s * rows + row) * 2];
-      const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);
-      l = fmaf(w, part_ml[(s * rows + row) * 2 + 1], l);
-      const float* po = part_o + (s * rows + row) * D + lane * V;
 #pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] = fmaf(w, po[i], acc[i]);
+    for (int s = 0; s < kMaxSplits; ++s) {  // fixed order: deterministic
+      const float w = (ml[s].x == -INFINITY) ? 0.f : fast_exp2(ml[s].x - m);
+      l = fmaf(w, ml[s].y, l);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fmaf(w, po[s][i], acc[i]);
     }
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     const int qi = static_cast<int>(row % S);

@@ -64,6 +64,7 @@ struct GemmParams {
   int m_tiles, n_tiles, total_units;
   int group_m;        // row-tiles per L2 group
   int mt_rotation;    // GEMM_PEER: row-tile this rank's walk starts at; 0 otherwise
+  int owner_tiles;    // GEMM_PEER: row-tiles per owner when the walk is dealt out over the owners in rounds; 0 otherwise
   int kv_merged;      // GEMM_QKV with at most 128 columns each of Wk and Wv: one tile holds both (K in accumulator
                       // columns [0,128), V in [128,256)) instead of two tiles that are three quarters empty
   int* err;
@@ -115,10 +116,19 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u, int rank
   const int rows_here = min(kGroupM, p.m_tiles - g * kGroupM);
   const int nt = rem / rows_here;
   int mt = g * kGroupM + (rem - nt * rows_here);
-  // GEMM_PEER: every rank starts its walk over the rows at its OWN rows and moves on from there, so that at any time
-  // the ranks send to different owners (a permutation over the links) instead of all to the same one
-  mt += p.mt_rotation;
-  if (mt >= p.m_tiles) mt -= p.m_tiles;
+  // GEMM_PEER: at any time the ranks send to different owners (a permutation over the links, not all to the same one).
+  // In rounds: position k * world + j of the walk is row-tile k of owner (rank + j) mod world, so that after round k
+  // EVERY owner has row-tile k from every rank and can reduce it while the projection goes on with round k + 1.
+  // (Row-tiles that do not divide among the owners: one rotation, every rank starting at its own rows.)
+  if (p.owner_tiles > 0) {
+    const int k = mt / p.world, j = mt - k * p.world;
+    int owner = p.rank + j;
+    if (owner >= p.world) owner -= p.world;
+    mt = owner * p.owner_tiles + k;
+  } else {
+    mt += p.mt_rotation;
+    if (mt >= p.m_tiles) mt -= p.m_tiles;
+  }
   r.m0 = PAIR ? (mt * 2 + rank) * BM : mt * BM;
   int src = 0;
   while (src + 1 < p.n_src && nt >= p.src_tile0[src + 1]) ++src;
@@ -815,7 +825,8 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.world = g.world; p.rank = g.rank; p.rows_per_rank = g.rows_per_rank;
   for (int r = 0; r < kMaxPeers; ++r) p.peer_counter[r] = g.peer_counter[r];
   if (g.mode == GEMM_PEER) {
-    p.mt_rotation = static_cast<int>(static_cast<long long>(g.rank) * p.m_tiles / g.world);
+    if (g.world > 1 && p.m_tiles % g.world == 0 && g.rows_per_rank % (pair ? 2 * BM : BM) == 0) p.owner_tiles = p.m_tiles / g.world;
+    else p.mt_rotation = static_cast<int>(static_cast<long long>(g.rank) * p.m_tiles / g.world);
     for (int r = 0; r < g.world; ++r) {  // this rank's slot of rank r's staging buffer: (rows_per_rank, N) 16-bit values
       const uint64_t dims[2] = {static_cast<uint64_t>(g.N[0]), static_cast<uint64_t>(g.rows_per_rank)};
       const uint64_t strides[1] = {static_cast<uint64_t>(g.N[0]) * 2};

@@ -8,7 +8,10 @@
 //      memory to a peer pointer, whole lines on the wire -- then arrives on the owner's counter for that block
 //      (red.release.sys, once the stores are complete).  The exchange a reduce-scatter would do after the GEMM
 //      travels during it.
-//   2. reduce_broadcast_kernel on every rank waits (bounded) per owned block until all ranks' warps have arrived, sums
+//      The ranks walk the row tiles in rounds (tile k of owner r, r+1, ... in round k), so after round k every owner
+//      has tile k from everybody.
+//   2. reduce_broadcast_kernel, launched behind the projection with programmatic stream serialisation, is resident
+//      beside it while it runs; every CTA waits (bounded) per owned block until all ranks' warps have arrived, sums
 //      the `world` staged contributions in rank order in fp32 (deterministic), adds the optional residual, rounds once
 //      and writes the block into EVERY rank's result buffer (the all-gather, again plain peer stores).  Its last CTA
 //      tells every peer that this rank's rows are complete and waits (bounded) for the same word from all peers, so
@@ -128,6 +131,9 @@ __global__ void __launch_bounds__(kRbThreads) reduce_broadcast_kernel(const Redu
         if (!wait_reaches(p.done[p.rank] + q, p.epoch, p.wait_limit, p.err, 602)) break;
     }
   }
+  // This kernel is launched while the projection before it still runs (see tb200_gemm_peer_reduce) and takes its
+  // order from the counters, not from that kernel's completion; it must still not END before the projection has.
+  pdl_wait();
 }
 
 }  // namespace
@@ -167,6 +173,7 @@ int tb200_gemm_peer_reduce(const tb200_peer_gemm_args* a, void* stream_) {
   auto done_of = [&](int r) { return reinterpret_cast<unsigned*>(static_cast<uint8_t*>(a->sync[r]) + 256); };
   auto counters_of = [&](int r) { return reinterpret_cast<unsigned*>(static_cast<uint8_t*>(a->sync[r]) + 768); };
 
+  ChainScope chain;
   GemmLaunch g;
   g.dtype = a->dtype;
   g.mode = GEMM_PEER;
@@ -199,9 +206,13 @@ int tb200_gemm_peer_reduce(const tb200_peer_gemm_args* a, void* stream_) {
   p.epoch = a->epoch;
   p.err = st->err_word;
   p.wait_limit = wait_limit_cycles();
-  if (a->dtype == TB200_BF16) reduce_broadcast_kernel<__nv_bfloat16><<<ctas, kRbThreads, 0, stream>>>(p);
-  else reduce_broadcast_kernel<__half><<<ctas, kRbThreads, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
+  // Chained to the projection: its CTAs (256 threads, no shared memory) become resident beside the projection's while
+  // that kernel runs -- all of whose CTAs are resident by then, so it never waits for an SM -- and each reduces its
+  // block as soon as the block's counter says that every rank's contribution has landed.
+  cudaError_t e;
+  if (a->dtype == TB200_BF16) e = launch_chained(reduce_broadcast_kernel<__nv_bfloat16>, dim3(ctas, 1, 1), dim3(kRbThreads, 1, 1), 0, stream, p);
+  else e = launch_chained(reduce_broadcast_kernel<__half>, dim3(ctas, 1, 1), dim3(kRbThreads, 1, 1), 0, stream, p);
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
 
 // ---- CUDA IPC plumbing for hosts that run one process per GPU: export a device allocation, open a peer's.
