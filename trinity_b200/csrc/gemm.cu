@@ -447,18 +447,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         n_total = p.src_n[t.src];
         float* prow = p.partial + (static_cast<long long>(t.split) * p.M + row) * p.ldp + col_base;
+        // A warp none of whose 32 rows exist (few-token blocks: most of the tile) reads nothing.  The others take 64
+        // columns per step, both loads in flight before the wait: with one tile per CTA nothing hides this loop.
+        const bool warp_has_rows = t.m0 + quad * 32 < p.M;
+        uint32_t r2[32];
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = t.n0 + c * 32;
+        for (int c = 0; warp_has_rows && c < BN / 64; ++c) {
+          const int col = t.n0 + c * 64;
           if (col >= n_total) break;
-          tmem_ld_x32(taddr + c * 32, r);
+          tmem_ld_x32(taddr + c * 64, r);
+          tmem_ld_x32(taddr + c * 64 + 32, r2);
           tmem_wait_ld();
           if (row_ok) {
-            const int valid = min(32, n_total - col);
+            const int valid = min(64, n_total - col);
             uint4* d = reinterpret_cast<uint4*>(prow + col);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               if (4 * i < valid) d[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (32 + 4 * i < valid) d[8 + i] = make_uint4(r2[4 * i], r2[4 * i + 1], r2[4 * i + 2], r2[4 * i + 3]);
           }
         }
       } else {  // GEMM_QKV
@@ -543,11 +551,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 }
 
 // ------------------------------------------------------------------ split-K finish
-template <typename T>
+template <typename T, bool GATED>
 __global__ void splitk_finish_kernel(SplitKFinish f) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int kBatch = 8;   // slices whose loads are in flight together: one slice at a time costs a trip to L2 each
+  // slices whose loads are in flight together: one slice at a time costs a trip to L2 each.  Sixteen cover the slice
+  // counts the library chooses in one trip (the 64-token down projection has nine); half as many with a gate
+  // tensor beside, whose loads double the registers
+  constexpr int kBatch = GATED ? 8 : 16;
   const int64_t groups_per_row = f.N / 8;
   const int64_t total = static_cast<int64_t>(f.M) * groups_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -565,7 +576,7 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
         const float* p = p0 + (on ? s0 + j : 0) * slice;
         x[j][0] = on ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
         x[j][1] = on ? __ldcg(reinterpret_cast<const float4*>(p + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (f.gated) {
+        if (GATED) {
           y[j][0] = on ? __ldcg(reinterpret_cast<const float4*>(p + f.N)) : make_float4(0.f, 0.f, 0.f, 0.f);
           y[j][1] = on ? __ldcg(reinterpret_cast<const float4*>(p + f.N + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -574,7 +585,7 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
       for (int j = 0; j < kBatch; ++j) {
         a[0] += x[j][0].x; a[1] += x[j][0].y; a[2] += x[j][0].z; a[3] += x[j][0].w;
         a[4] += x[j][1].x; a[5] += x[j][1].y; a[6] += x[j][1].z; a[7] += x[j][1].w;
-        if (f.gated) {
+        if (GATED) {
           b[0] += y[j][0].x; b[1] += y[j][0].y; b[2] += y[j][0].z; b[3] += y[j][0].w;
           b[4] += y[j][1].x; b[5] += y[j][1].y; b[6] += y[j][1].z; b[7] += y[j][1].w;
         }
@@ -585,7 +596,7 @@ __global__ void splitk_finish_kernel(SplitKFinish f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float x = a[j] * rs;
-      if (f.gated) x = silu(x) * (b[j] * rs);
+      if (GATED) x = silu(x) * (b[j] * rs);
       if (f.act == 1) x = gelu_erf(x);
       v[j] = x;
     }
@@ -874,8 +885,12 @@ int launch_splitk_finish(const SplitKFinish& f, cudaStream_t stream) {
   if (blocks > st->num_sms * 8) blocks = st->num_sms * 8;
   const dim3 grid(static_cast<unsigned>(blocks), 1, 1), block(threads, 1, 1);
   cudaError_t e;
-  if (f.dtype == TB200_BF16) e = launch_chained(splitk_finish_kernel<__nv_bfloat16>, grid, block, 0, stream, f);
-  else if (f.dtype == TB200_F16) e = launch_chained(splitk_finish_kernel<__half>, grid, block, 0, stream, f);
+  if (f.dtype == TB200_BF16)
+    e = f.gated ? launch_chained(splitk_finish_kernel<__nv_bfloat16, true>, grid, block, 0, stream, f)
+                : launch_chained(splitk_finish_kernel<__nv_bfloat16, false>, grid, block, 0, stream, f);
+  else if (f.dtype == TB200_F16)
+    e = f.gated ? launch_chained(splitk_finish_kernel<__half, true>, grid, block, 0, stream, f)
+                : launch_chained(splitk_finish_kernel<__half, false>, grid, block, 0, stream, f);
   else return TB200_ERR_UNSUPPORTED;
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_CUDA;
 }
