@@ -38,6 +38,16 @@ class Fp32Ops:
         return orc.rmsnorm(a, weight, eps)
 
 
+def _teardown():
+    """Leave the group without turning a peer's earlier exit into a failure: gloo's teardown raises when the other side
+    has already closed its sockets, which says nothing about the result a rank has long handed back."""
+    try:
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -64,7 +74,7 @@ def _ffn_worker(rank, world, port, case, ret):
         if rank == 0:
             ret.put({k: v.clone() for k, v in out.items()})
     finally:
-        dist.destroy_process_group()
+        _teardown()
 
 
 @pytest.mark.parametrize("case", ["plain", "gelu", "block", "tail", "plain3", "tail5"])
@@ -110,7 +120,7 @@ def _attn_worker(rank, world, port, ret):
         if rank == 0:
             ret.put((full.clone(), out["C_out1"].clone()))
     finally:
-        dist.destroy_process_group()
+        _teardown()
 
 
 def test_head_group_sharded_attention_two_ranks():
@@ -141,7 +151,7 @@ def _evict_worker(rank, world, port, ret):
         out = shard.evict_rows(k, v, idx, kv_len=40, keep_recent=3, compact=orc.kv_compact)
         ret.put((rank, out["rows"].start, out["rows"].stop, out["k"].clone(), out["kept_pos"].clone(), out["all_new_len"].clone()))
     finally:
-        dist.destroy_process_group()
+        _teardown()
 
 
 def _evict_inputs():
