@@ -223,4 +223,4 @@ def test_all_reduce_with_an_absent_rank_raises_instead_of_hanging():
         assert not p.is_alive(), "a rank hung"
     assert ret[1] == "absent"
     kind, waited, msg = ret[0]
-    assert kind == "timeout" and 0.9 < waited < 2.5 and "did not complete" in msg
+    assert kind == "timeout" and 0.9 < waited < 8.0 and "did not complete" in msg

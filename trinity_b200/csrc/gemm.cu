@@ -65,6 +65,9 @@ struct GemmParams {
   int group_m;        // row-tiles per L2 group
   int mt_rotation;    // GEMM_PEER: row-tile this rank's walk starts at; 0 otherwise
   int owner_tiles;    // GEMM_PEER: row-tiles per owner when the walk is dealt out over the owners in rounds; 0 otherwise
+  int rows64;         // M <= 64: the tile is 64 rows tall (tcgen05.mma with M = 64, A boxes of 64 rows): half the tensor-core
+                      // work of a 128-row tile that is half padding -- these shapes run under the power cap, where that work
+                      // costs SM clock -- and all four epilogue warps get rows (16 each) instead of two (32 each)
   int kv_merged;      // GEMM_QKV with at most 128 columns each of Wk and Wv: one tile holds both (K in accumulator
                       // columns [0,128), V in [128,256)) instead of two tiles that are three quarters empty
   int* err;
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (with_a) tma_load_2d_pair(sa, &p.map_a, fb, kb * BK, t.m0);
       } else {
         if (with_b) {
-          mbar_arrive_expect_tx(&full[stage], SB);
+          mbar_arrive_expect_tx(&full[stage], p.rows64 ? SB - kABytes / 2 : SB);   // a 64-row A box is half the bytes
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             int src = t.src, col = t.n0 + 64 * c;
@@ -283,7 +286,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     }
   } else if (warp == 1 && rank == 0) {
     // ------------------------------------------------------------ MMA issuer (a pair's leader issues for both CTAs)
-    constexpr uint32_t idesc = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, PAIR ? 2 * BM : BM, BN);
+    constexpr uint32_t idesc_full = make_idesc(IsBf16<T>::value, /*a_mn=*/false, /*b_mn=*/true, PAIR ? 2 * BM : BM, BN);
+    constexpr uint32_t idesc_64 = make_idesc(IsBf16<T>::value, false, true, 64, BN);
+    const uint32_t idesc = (!PAIR && p.rows64) ? idesc_64 : idesc_full;
     pdl_wait();
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
@@ -331,8 +336,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       const Unit t = decode_unit<PAIR>(p, u, rank);
       if (!wait_bar<PAIR>(&tfull[acc], acc_phase, ctx, 104)) break;
       tc_fence_after();
-      const int row = t.m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
+      // A 128-row accumulator has row i in TMEM lane i.  A 64-row one (M = 64) has rows [16 q, 16 q + 16) in the first
+      // sixteen lanes of quadrant q: every epilogue warp owns sixteen rows, its upper sixteen lanes hold nothing.
+      const int row = p.rows64 ? t.m0 + quad * 16 + (lane & 15) : t.m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M && (!p.rows64 || lane < 16);
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.f;
       uint32_t r[32];
@@ -449,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         float* prow = p.partial + (static_cast<long long>(t.split) * p.M + row) * p.ldp + col_base;
         // A warp none of whose 32 rows exist (few-token blocks: most of the tile) reads nothing.  The others take 64
         // columns per step, both loads in flight before the wait: with one tile per CTA nothing hides this loop.
-        const bool warp_has_rows = t.m0 + quad * 32 < p.M;
+        const bool warp_has_rows = t.m0 + quad * (p.rows64 ? 16 : 32) < p.M;
         uint32_t r2[32];
 #pragma unroll 1
         for (int c = 0; warp_has_rows && c < BN / 64; ++c) {
@@ -851,9 +858,10 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   p.ldp = ldp;
 
   {
+    p.rows64 = (!pair && g.M <= 64 && g.mode != GEMM_PEER) ? 1 : 0;
     const uint64_t dims[2] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(g.K) * 2};
-    const uint32_t box[2] = {BK, BM};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(p.rows64 ? 64 : BM)};
     if ((status = make_tensor_map(&p.map_a, g.A, 2, dims, strides, box)) != TB200_OK) return status;
   }
   for (int s = 0; s < g.n_src; ++s) {
@@ -1009,9 +1017,10 @@ int gemm_splitk_static(const tb200_gemm_args* a, cudaStream_t stream) {
   p.partial = scratch;
   p.ldp = static_cast<long long>(n_src) * N;
   {
+    p.rows64 = M <= 64 ? 1 : 0;
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {BK, BM};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(p.rows64 ? 64 : BM)};
     if ((status = make_tensor_map(&p.map_a, a->a, 2, dims, strides, box)) != TB200_OK) return status;
   }
   const void* srcs[2] = {a->b, a->b2};
