@@ -58,6 +58,9 @@ def _gemm_ref(a, b, b2=None, rs=None, res=None, act=0):
     (384, 512, 512, dict(rs=True, res=True)), (384, 1024, 520, dict(gelu=True)), (300, 640, 1024, dict(gated=True, rs=True)),
     (130, 136, 72, dict(gated=True)), (64, 4096, 2048, dict(split=4)), (64, 1024, 2048, dict(split=4, gated=True, rs=True)),
     (16, 512, 4096, dict(split=0, res=True)), (16, 512, 4096, dict(split=7, gelu=True, res=True)), (2100, 520, 136, {}),
+    # either side of the 64-row tile (at most 64 rows: sixteen per epilogue warp; more: thirty-two)
+    (63, 264, 128, dict(res=True, rs=True)), (65, 264, 128, dict(res=True, rs=True)), (33, 520, 1024, dict(gated=True, split=2)),
+    (17, 256, 512, dict(gelu=True)), (49, 136, 200, dict(gated=True, rs=True)),
 ])
 def test_gemm(ops, dt, M, N, K, opts):
     g = torch.Generator().manual_seed(M + N + K)
