@@ -14,11 +14,11 @@
 //            each group also appends those rows to the caches.  The loads of the cached keys are already in flight
 //            by then: they are issued before the wait for the projection kernel, which does not write them.
 //   main     warp w takes the 16-key chunks w, w+8, ... of the share: TMA boxes into its own two-deep ring, one
-//            mbarrier per stage (no CTA-wide barrier), S = Q K^T (Q fragments stay in registers), online softmax in the log2 domain,
-//            O += P V with P taken straight from the S accumulators
+//            mbarrier per stage (no CTA-wide barrier), S = Q K^T (Q fragments stay in registers), online softmax in
+//            the log2 domain, O += P V with P taken straight from the S accumulators
 //   merge    the eight warps' (m, l, O) through shared memory, then the C shares through distributed shared memory:
 //            CTA r of the cluster reads column slice r of every share, in rank order, and writes those columns of O2
-// Nothing goes through global scratch and nothing waits on another CTA except at the two cluster barriers.
+// Nothing goes through global scratch and nothing waits on another CTA except at the cluster's barriers.
 // Every order of summation is fixed: results are bit-identical from run to run.
 //
 // Bound: launch and memory latency (K and V of the cache once per q head: 17 MB at the benchmark point, 3 us of HBM
@@ -36,7 +36,7 @@ constexpr int kDecWarps = 8;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecRows = 16;     // query rows of a block (S <= 16; the rest are zero)
 constexpr int kDecChunk = 16;    // keys per warp step
-constexpr int kDecStages = 2;    // chunks in flight per warp (a third stage would leave room for one CTA per SM only)
+constexpr int kDecStages = 2;    // chunks in flight per warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
