@@ -13,7 +13,7 @@
 //            fixed order, row scale, optional per-head RMSNorm -- what qkv_finish_kernel does.  The first q head of
 //            each group also appends those rows to the caches.  The loads of the cached keys are already in flight
 //            by then: they are issued before the wait for the projection kernel, which does not write them.
-//   main     warp w takes the 16-key chunks w, w+8, ... of the share: TMA boxes into its own two-deep ring, one
+//   main     warp w takes the 16-key chunks w, w+8, ... of the share: TMA boxes into its own three-deep ring, one
 //            mbarrier per stage (no CTA-wide barrier), S = Q K^T (Q fragments stay in registers), online softmax in
 //            the log2 domain, O += P V with P taken straight from the S accumulators
 //   merge    the eight warps' (m, l, O) through shared memory, then the C shares through distributed shared memory:
@@ -36,7 +36,7 @@ constexpr int kDecWarps = 8;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecRows = 16;     // query rows of a block (S <= 16; the rest are zero)
 constexpr int kDecChunk = 16;    // keys per warp step
-constexpr int kDecStages = 2;    // chunks in flight per warp
+constexpr int kDecStages = 3;    // chunks in flight per warp: at the benchmark point (two or three chunks per warp) all of them, before q is even finished
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
