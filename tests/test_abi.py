@@ -165,3 +165,12 @@ def test_wait_limit_is_a_host_setting(lib):
     assert lib.tb200_set_wait_limit_cycles(1_000_000) == 0
     assert lib.tb200_get_wait_limit_cycles() == 1_000_000
     assert lib.tb200_set_wait_limit_cycles(4_000_000_000) == 0
+
+
+def test_chained_launch_is_a_host_setting(lib):
+    """On by default; the setter returns what was set before (no device involved)."""
+    assert lib.tb200_set_chained_launch(0) == 1
+    assert lib.tb200_set_chained_launch(0) == 0
+    assert lib.tb200_set_chained_launch(1) == 0
+    assert lib.tb200_set_chained_launch(7) == 1                     # any non-zero value means on
+    assert lib.tb200_set_chained_launch(1) == 1
